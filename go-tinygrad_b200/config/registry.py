@@ -19,8 +19,8 @@ from .llama import ConfigError
 
 @dataclass(frozen=True)
 class Architecture:
-    """`names` are matched against config.json's ``architectures`` entries and
-    ``model_type``.  `read_config(raw_json) -> config`; `plan(config) -> ModelPlan`.
+    """`names` are matched against config.json's ``architectures`` entries,
+    ``architecture`` and ``model_type``.  `read_config(raw_json) -> config`; `plan(config) -> ModelPlan`.
     `ignore`: shell-style patterns of tensor names a checkpoint of this
     architecture may carry that no part reads (stored buffers and the like); a
     tensor that neither a part declares nor a pattern matches is still an error."""
@@ -53,16 +53,18 @@ def registered_architectures() -> Tuple[str, ...]:
 
 
 def find_architecture(raw: Mapping[str, Any]) -> Architecture:
-    """The entry for a parsed config.json: ``architectures`` first, then ``model_type``."""
+    """The entry for a parsed config.json: ``architectures`` (a list) first, then
+    ``architecture`` (one name), then ``model_type``."""
     candidates = []
     archs = raw.get("architectures")
     if isinstance(archs, (list, tuple)):
         candidates += [str(a) for a in archs]
-    if raw.get("model_type"):
-        candidates.append(str(raw["model_type"]))
+    for key in ("architecture", "model_type"):
+        if raw.get(key):
+            candidates.append(str(raw[key]))
     if not candidates:
         raise ConfigError("config.json names no architecture: it has neither "
-                          "'architectures' nor 'model_type'")
+                          "'architectures', 'architecture' nor 'model_type'")
     for name in candidates:
         if name in _ARCHITECTURES:
             return _ARCHITECTURES[name]

@@ -189,8 +189,10 @@ GTG_API int gtg_swiglu(int dtype, const void* gu, void* out, int M, int I, cudaS
 // cos_sin[n,i] = (cos, sin)(positions[n] * inv_freq[i]); the angle is a double
 // product and the functions are evaluated in double, then rounded to float
 // (model/llama.go:855-862).  Computed once per step for the step's tokens.
+// `amplitude` multiplies both (1 for a plain rotation; frequency scalings that
+// lengthen the context may grow queries and keys a little with it).
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
-                                  float2* __restrict__ cos_sin, int N, int half) {
+                                  float2* __restrict__ cos_sin, int N, int half, double amplitude) {
     chain_release();
     chain_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -199,15 +201,15 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const doubl
     const double ang = (double)positions[n] * inv_freq[i];
     double s, c;
     sincos(ang, &s, &c);
-    cos_sin[idx] = make_float2((float)c, (float)s);
+    cos_sin[idx] = make_float2((float)(c * amplitude), (float)(s * amplitude));
 }
 
 GTG_API int gtg_rope_table(const int* positions, const double* inv_freq, float* cos_sin,
-                           int N, int half, cudaStream_t stream) {
+                           int N, int half, double amplitude, cudaStream_t stream) {
     int st = 0;
     if (N <= 0 || half <= 0) return 0;
     const int total = N * half;
-    st = launch_chained(rope_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, positions, inv_freq, (float2*)cos_sin, N, half);
+    st = launch_chained(rope_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, positions, inv_freq, (float2*)cos_sin, N, half, amplitude);
     return st;
 }
 
@@ -220,10 +222,12 @@ GTG_API int gtg_rope_table(const int* positions, const double* inv_freq, float* 
 // interleaved, (2i, 2i+1); `rot` <= hd channels of a head rotate, the rest pass
 // unchanged.  cos_sin holds rot/2 (cos, sin) per token.  With n_kv_store == 0
 // only the queries are rotated (a layer that reads another layer's cache).
-// cos_sin == nullptr means no rotation.
+// cos_sin == nullptr means no rotation.  With `v_from_k` the row has no value
+// heads: the value stored for a key/value head is its key as projected, before
+// the rotation (a mixer without a value projection).
 template <typename T>
 __global__ void rope_kv_store_kernel(T* __restrict__ qkv, int ld, const float2* __restrict__ cos_sin,
-                                     int n_heads, int n_kv_store, int hd, int rot, int interleaved,
+                                     int n_heads, int n_kv_store, int hd, int rot, int interleaved, int v_from_k,
                                      T* __restrict__ kc, T* __restrict__ vc, long long page_stride,
                                      const int* __restrict__ block_table, int table_stride,
                                      const int* __restrict__ token_seq, const int* __restrict__ slots,
@@ -245,7 +249,7 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, int ld, const float2* 
     const int items = (n_heads + 2 * n_kv_store) * half;
     for (int it = threadIdx.x; it < items; it += blockDim.x) {
         const int head = it / half, i = it - head * half;
-        T* src = row + head * hd;
+        T* src = row + (v_from_k && head >= n_heads + n_kv_store ? head - n_kv_store : head) * hd;
         int ia, ib;
         if (i < rhalf) { ia = interleaved ? 2 * i : i; ib = interleaved ? 2 * i + 1 : i + rhalf; }
         else { ia = rot + 2 * (i - rhalf); ib = ia + 1; }
@@ -272,7 +276,7 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, int ld, const float2* 
 // The same for bfloat16 with head sizes that are multiples of 16 and 16-byte
 // aligned rows: one thread rotates 8 consecutive pairs with 16-byte accesses.
 __global__ void rope_kv_store_bf16_vec_kernel(bf16* __restrict__ qkv, int ld, const float2* __restrict__ cos_sin,
-                                              int n_heads, int n_kv_store, int hd,
+                                              int n_heads, int n_kv_store, int hd, int v_from_k,
                                               bf16* __restrict__ kc, bf16* __restrict__ vc, long long page_stride,
                                               const int* __restrict__ block_table, int table_stride,
                                               const int* __restrict__ token_seq, const int* __restrict__ slots,
@@ -292,7 +296,7 @@ __global__ void rope_kv_store_bf16_vec_kernel(bf16* __restrict__ qkv, int ld, co
     const int items = (n_heads + 2 * n_kv_store) * chunks;
     for (int it = threadIdx.x; it < items; it += blockDim.x) {
         const int head = it / chunks, i = (it - head * chunks) * 8;
-        bf16* src = row + head * hd;
+        bf16* src = row + (v_from_k && head >= n_heads + n_kv_store ? head - n_kv_store : head) * hd;
         const uint4 av = *reinterpret_cast<const uint4*>(src + i);
         const uint4 bv = *reinterpret_cast<const uint4*>(src + i + half);
         if (head >= n_heads + n_kv_store) {                       // a value head: copy
@@ -323,7 +327,7 @@ __global__ void rope_kv_store_bf16_vec_kernel(bf16* __restrict__ qkv, int ld, co
 }
 
 GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin,
-                              int n_heads, int n_kv_store, int hd, int rot, int interleaved,
+                              int n_heads, int n_kv_store, int hd, int rot, int interleaved, int v_from_k,
                               void* kc, void* vc, long long page_stride,
                               const int* block_table, int table_stride,
                               const int* token_seq, const int* slots, const int* positions,
@@ -336,7 +340,7 @@ GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin
         const int vec_items = (n_heads + 2 * n_kv_store) * (hd / 16);
         int t = 32;
         while (t < 256 && t < vec_items) t *= 2;
-        st = launch_chained(rope_kv_store_bf16_vec_kernel, dim3(N), dim3(t), 0, stream, (bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
+        st = launch_chained(rope_kv_store_bf16_vec_kernel, dim3(N), dim3(t), 0, stream, (bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd, v_from_k,
             (bf16*)kc, (bf16*)vc, page_stride, block_table, table_stride, token_seq, slots, positions);
         return st;
     }
@@ -344,10 +348,10 @@ GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin
     int threads = 64;
     while (threads < 512 && threads < items) threads *= 2;
     if (dtype == 0)
-        st = launch_chained(rope_kv_store_kernel<float>, dim3(N), dim3(threads), 0, stream, (float*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd, rot, interleaved,
+        st = launch_chained(rope_kv_store_kernel<float>, dim3(N), dim3(threads), 0, stream, (float*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd, rot, interleaved, v_from_k,
             (float*)kc, (float*)vc, page_stride, block_table, table_stride, token_seq, slots, positions);
     else if (dtype == 1)
-        st = launch_chained(rope_kv_store_kernel<bf16>, dim3(N), dim3(threads), 0, stream, (bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd, rot, interleaved,
+        st = launch_chained(rope_kv_store_kernel<bf16>, dim3(N), dim3(threads), 0, stream, (bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd, rot, interleaved, v_from_k,
             (bf16*)kc, (bf16*)vc, page_stride, block_table, table_stride, token_seq, slots, positions);
     else return kErrBadArgument;
     return st;
@@ -429,4 +433,148 @@ GTG_API int gtg_check_cache_access(int mode, int n_items, const int* token_seq, 
     check_cache_access_kernel<<<(n_items + 127) / 128, 128, 0, stream>>>(mode, n_items, token_seq, slots, positions,
         start_pos, cu_seqlens, n_seqs, block_table, table_stride, n_slots, n_pages, flag);
     return launch_status();
+}
+
+// ------------------------------------------------- residual add + LayerNorm
+// x = residual[r,:] (+ pending[r,:]);  out[i,:] = (x - mean) / sqrt(var + eps) * weight + bias,
+// var the mean of the squared deviations from the mean (two passes over the row,
+// which is kept in shared memory), everything in float.  Rows as in add_rmsnorm.
+template <typename T>
+__global__ void add_layernorm_kernel(float* __restrict__ residual, const T* __restrict__ pending,
+                                     const float* __restrict__ weight, const float* __restrict__ bias, float eps,
+                                     T* __restrict__ out, const int* __restrict__ rows, int H) {
+    chain_release();
+    chain_wait();
+    extern __shared__ float smem[];
+    float* row = smem;          // H floats
+    float* scratch = smem + H;  // 33 floats
+    const int i_out = blockIdx.x;
+    const int r = rows ? rows[i_out] : i_out;
+    float* res = residual + (size_t)r * H;
+    const T* pen = pending ? pending + (size_t)r * H : nullptr;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float x = res[i];
+        if (pen) {
+            x += to_f32<T>(pen[i]);
+            if (!rows) res[i] = x;
+        }
+        row[i] = x;
+        sum += x;
+    }
+    const float mean = block_sum(sum, scratch) / (float)H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float d = row[i] - mean;
+        ss += d * d;
+    }
+    const float var = block_sum(ss, scratch) / (float)H;
+    const float s = 1.0f / sqrtf(var + eps);
+    T* o = out + (size_t)i_out * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        o[i] = from_f32<T>((row[i] - mean) * s * weight[i] + (bias ? bias[i] : 0.f));
+}
+
+GTG_API int gtg_add_layernorm(int dtype, float* residual, const void* pending, const float* weight,
+                              const float* bias, float eps, void* out, const int* rows, int R, int H,
+                              cudaStream_t stream) {
+    if (R <= 0) return 0;
+    int threads = 32;
+    while (threads < 1024 && threads * 4 < H) threads *= 2;
+    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    if (smem > 200 * 1024) return kErrUnsupported;
+    cudaError_t e;
+    if (dtype == 0) {
+        if (smem > 48 * 1024) {
+            e = cudaFuncSetAttribute(add_layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return launch_chained(add_layernorm_kernel<float>, dim3(R), dim3(threads), smem, stream, residual, (const float*)pending, weight, bias, eps, (float*)out, rows, H);
+    }
+    if (dtype == 1) {
+        if (smem > 48 * 1024) {
+            e = cudaFuncSetAttribute(add_layernorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return launch_chained(add_layernorm_kernel<bf16>, dim3(R), dim3(threads), smem, stream, residual, (const bf16*)pending, weight, bias, eps, (bf16*)out, rows, H);
+    }
+    return kErrBadArgument;
+}
+
+// ------------------------------------------------------ pointwise activations
+// x <- f(x) in place, evaluated in float.  kind 0: relu(x)^2; 1: gelu in its tanh
+// form, 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))); 2: silu, x / (1 + exp(-x)).
+__device__ __forceinline__ float activate(float x, int kind) {
+    if (kind == 0) { const float r = fmaxf(x, 0.f); return r * r; }
+    if (kind == 1) return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    return x / (1.0f + expf(-x));
+}
+
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ x, int ld, int M, int I, int kind) {
+    chain_release();
+    chain_wait();
+    const size_t total = (size_t)M * I;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t m = idx / I;
+        T* p = x + m * ld + (idx - m * I);
+        *p = from_f32<T>(activate(to_f32<T>(*p), kind));
+    }
+}
+
+GTG_API int gtg_activation(int dtype, void* x, int ld, int M, int I, int kind, cudaStream_t stream) {
+    if (M <= 0 || I <= 0) return 0;
+    if (kind < 0 || kind > 2 || ld < I) return kErrBadArgument;
+    const size_t total = (size_t)M * I;
+    int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    if (dtype == 0) return launch_chained(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, ld, M, I, kind);
+    if (dtype == 1) return launch_chained(activation_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, ld, M, I, kind);
+    return kErrBadArgument;
+}
+
+// ------------------------------------------------------------- soft cap
+// x <- cap * tanh(x / cap) on float logits, in place.
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap) {
+    chain_release();
+    chain_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        x[idx] = cap * tanhf(x[idx] / cap);
+}
+
+GTG_API int gtg_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (!(cap > 0.f)) return kErrBadArgument;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+    return launch_chained(softcap_kernel, dim3(blocks), dim3(256), 0, stream, x, (size_t)total, cap);
+}
+
+// ---------------------------------------- hidden state beside a kept tensor
+// out[n, 0:H] = residual[n,:] (+ pending[n,:]);  out[n, H:2H] = other[n,:]: the
+// operand of a projection that mixes the hidden state with a tensor kept from
+// earlier in the step (the embedding output).  The sum is float; out is the
+// compute type.
+template <typename T>
+__global__ void hidden_concat_kernel(const float* __restrict__ residual, const T* __restrict__ pending,
+                                     const float* __restrict__ other, T* __restrict__ out, int H) {
+    chain_release();
+    chain_wait();
+    const size_t n = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float x = residual[n * H + i];
+        if (pending) x += to_f32<T>(pending[n * H + i]);
+        out[n * 2 * H + i] = from_f32<T>(x);
+        out[n * 2 * H + H + i] = from_f32<T>(other[n * H + i]);
+    }
+}
+
+GTG_API int gtg_hidden_concat(int dtype, const float* residual, const void* pending, const float* other,
+                              void* out, int N, int H, cudaStream_t stream) {
+    if (N <= 0 || H <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == 0) return launch_chained(hidden_concat_kernel<float>, dim3(N), dim3(threads), 0, stream, residual, (const float*)pending, other, (float*)out, H);
+    if (dtype == 1) return launch_chained(hidden_concat_kernel<bf16>, dim3(N), dim3(threads), 0, stream, residual, (const bf16*)pending, other, (bf16*)out, H);
+    return kErrBadArgument;
 }

@@ -9,9 +9,10 @@
 namespace {
 constexpr int BM = 64, BN = 64, BK = 16, PAD = 4;
 
+template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
-gemm_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw,
-                float* __restrict__ C, int ldc, int M, int N, int K) {
+gemm_simt_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, int ldw,
+                 TC* __restrict__ C, int ldc, int M, int N, int K) {
     __shared__ float As[BK][BM + PAD];
     __shared__ float Ws[BK][BN + PAD];
     const int tid = threadIdx.x;
@@ -29,8 +30,8 @@ gemm_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
         for (int j = 0; j < 4; ++j) {
             const int k = k0 + lk + j;
             const int am = m0 + lrow, wn = n0 + lrow;
-            As[lk + j][lrow] = (am < M && k < K) ? A[(size_t)am * lda + k] : 0.f;
-            Ws[lk + j][lrow] = (wn < N && k < K) ? W[(size_t)wn * ldw + k] : 0.f;
+            As[lk + j][lrow] = (am < M && k < K) ? to_f32<TA>(A[(size_t)am * lda + k]) : 0.f;
+            Ws[lk + j][lrow] = (wn < N && k < K) ? to_f32<TA>(W[(size_t)wn * ldw + k]) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -54,7 +55,7 @@ gemm_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
-            if (n < N) C[(size_t)m * ldc + n] = acc[i][j];
+            if (n < N) C[(size_t)m * ldc + n] = from_f32<TC>(acc[i][j]);
         }
     }
 }
@@ -66,6 +67,23 @@ GTG_API int gtg_gemm_f32(const float* A, int lda, const float* W, int ldw, float
     if (K <= 0 || lda < K || ldw < K || ldc < N) return kErrBadArgument;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return kErrUnsupported;
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, M, N, K);
+    gemm_simt_kernel<float, float><<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, M, N, K);
+    return launch_status();
+}
+
+// The same walk for bfloat16 operands of any size and alignment (float
+// accumulation; the result bfloat16 or float): the route of shapes that the
+// tensor-core products refuse (an inner size or a row stride that is no
+// multiple of 8 elements).
+GTG_API int gtg_gemm_bf16_simt(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_f32,
+                               int M, int N, int K, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || lda < K || ldw < K || ldc < N) return kErrBadArgument;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    if (grid.y > 65535) return kErrUnsupported;
+    if (out_f32)
+        gemm_simt_kernel<bf16, float><<<grid, 256, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, ldw, (float*)C, ldc, M, N, K);
+    else
+        gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, ldw, (bf16*)C, ldc, M, N, K);
     return launch_status();
 }

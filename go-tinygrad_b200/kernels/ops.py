@@ -8,7 +8,7 @@ is no other route for the same work (no library attention, no CPU path).
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from ctypes import c_double, c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
 
 import torch
@@ -17,15 +17,24 @@ from . import build
 
 PAGE_TOKENS = 64
 
-_P, _I, _L, _F, _U = c_void_p, c_int, c_longlong, c_float, c_ulonglong
+_P, _I, _L, _F, _U, _D = c_void_p, c_int, c_longlong, c_float, c_ulonglong, c_double
 
 # library, symbol -> argument types (the stream is always last)
 _SIGNATURES = {
     "gtg_embed": ("elementwise", [_I, _P, _P, _P, _I, _I, _I, _P]),
     "gtg_add_rmsnorm": ("elementwise", [_I, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
     "gtg_swiglu": ("elementwise", [_I, _P, _P, _I, _I, _P]),
-    "gtg_rope_table": ("elementwise", [_P, _P, _P, _I, _I, _P]),
-    "gtg_rope_kv_store": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P]),
+    "gtg_rope_table": ("elementwise", [_P, _P, _P, _I, _I, _D, _P]),
+    "gtg_rope_kv_store": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P]),
+    "gtg_add_layernorm": ("elementwise", [_I, _P, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
+    "gtg_activation": ("elementwise", [_I, _P, _I, _I, _I, _I, _P]),
+    "gtg_softcap": ("elementwise", [_P, _L, _F, _P]),
+    "gtg_hidden_concat": ("elementwise", [_I, _P, _P, _P, _P, _I, _I, _P]),
+    "gtg_causal_conv_silu": ("ssm", [_I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _P]),
+    "gtg_conv_state_update": ("ssm", [_I, _P, _I, _P, _P, _P, _I, _I, _I, _P]),
+    "gtg_ssm_scan": ("ssm", [_I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_gated_rmsnorm": ("ssm", [_I, _P, _I, _P, _I, _P, _F, _P, _I, _I, _I, _I, _P]),
+    "gtg_gemm_bf16_simt": ("gemm_f32", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_advance": ("elementwise", [_P, _P, _P, _P, _I, _P]),
     "gtg_check_cache_access": ("elementwise", [_I, _I, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _P, _P]),
     "gtg_gemm_f32": ("gemm_f32", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
@@ -262,14 +271,14 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     _check(_fn("gtg_swiglu")(_dt(out), _ptr(gate_up), _ptr(out), M, two_i // 2, _stream()), "swiglu")
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
-    """out[n,i] = (cos, sin)(positions[n] * inv_freq[i]), angle and functions in float64."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor, amplitude: float = 1.0) -> None:
+    """out[n,i] = amplitude * (cos, sin)(positions[n] * inv_freq[i]), angle and functions in float64."""
     N, half = positions.numel(), inv_freq.numel()
     _need(positions.dtype == torch.int32 and positions.is_contiguous(), "rope_table: positions must be int32")
     _need(inv_freq.dtype == torch.float64 and inv_freq.is_contiguous(), "rope_table: inv_freq must be float64")
     _need(out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (N, half, 2),
           "rope_table: out must be float32 [N, half, 2]")
-    _check(_fn("gtg_rope_table")(_ptr(positions), _ptr(inv_freq), _ptr(out), N, half, _stream()), "rope_table")
+    _check(_fn("gtg_rope_table")(_ptr(positions), _ptr(inv_freq), _ptr(out), N, half, float(amplitude), _stream()), "rope_table")
 
 
 ROTARY_PAIRINGS = {"half": 0, "interleaved": 1}
@@ -277,13 +286,16 @@ ROTARY_PAIRINGS = {"half": 0, "interleaved": 1}
 
 def rope_kv_store(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], n_heads: int, n_kv_store: int,
                   head_dim: int, kv, token_seq: torch.Tensor, slots: torch.Tensor,
-                  positions: torch.Tensor, pairing: str = "half", rotary_dim: Optional[int] = None) -> None:
+                  positions: torch.Tensor, pairing: str = "half", rotary_dim: Optional[int] = None,
+                  values_from_keys: bool = False) -> None:
     """Rotate the query heads of qkv in place; rotate the key heads and copy the
     value heads into the cache `kv` at each token's (slot, position).  With
     n_kv_store == 0 only queries are rotated and `kv` may be None.  `pairing`:
     "half" rotates channel i with i + rotary_dim/2, "interleaved" 2i with 2i+1;
     the first `rotary_dim` channels of a head rotate (default: all), the rest
-    pass unchanged.  Any other layout is refused."""
+    pass unchanged.  Any other layout is refused.  With `values_from_keys` qkv
+    holds query and key heads only, and the value stored for a head is its key
+    as projected, before the rotation."""
     _rows2d(qkv, "rope_kv_store: qkv")
     N = qkv.shape[0]
     _need(head_dim % 2 == 0, "rope_kv_store: head_dim must be even")
@@ -292,7 +304,8 @@ def rope_kv_store(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], n_heads: i
     rot = head_dim if rotary_dim is None else int(rotary_dim)
     _need(rot % 2 == 0 and 0 < rot <= head_dim,
           f"rope_kv_store: rotary_dim {rot} must be even and between 2 and head_dim {head_dim}")
-    _need(qkv.shape[1] >= (n_heads + 2 * n_kv_store) * head_dim, "rope_kv_store: qkv is too narrow")
+    _need(qkv.shape[1] >= (n_heads + (1 if values_from_keys else 2) * n_kv_store) * head_dim,
+          "rope_kv_store: qkv is too narrow")
     if cos_sin is not None:
         _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
               and tuple(cos_sin.shape) == (N, rot // 2, 2), "rope_kv_store: cos_sin must be float32 [N, rotary_dim/2, 2]")
@@ -306,7 +319,7 @@ def rope_kv_store(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], n_heads: i
     else:
         args = (None, None, 0, None, 0)
     _check(_fn("gtg_rope_kv_store")(_dt(qkv), _ptr(qkv), qkv.stride(0), _ptr(cos_sin), n_heads, n_kv_store,
-                                    head_dim, rot, ROTARY_PAIRINGS[pairing], *args, _ptr(token_seq), _ptr(slots), _ptr(positions),
+                                    head_dim, rot, ROTARY_PAIRINGS[pairing], 1 if values_from_keys else 0, *args, _ptr(token_seq), _ptr(slots), _ptr(positions),
                                     N, _stream()), "rope_kv_store")
 
 
@@ -317,6 +330,141 @@ def advance(tokens: torch.Tensor, positions: torch.Tensor, steps: torch.Tensor,
     for name, t in (("tokens", tokens), ("positions", positions), ("steps", steps), ("sampled", sampled)):
         _need(t.dtype == torch.int32 and t.is_contiguous() and t.numel() >= B, f"advance: {name} must be int32 [B]")
     _check(_fn("gtg_advance")(_ptr(tokens), _ptr(positions), _ptr(steps), _ptr(sampled), B, _stream()), "advance")
+
+
+
+def add_layernorm(residual: torch.Tensor, pending: Optional[torch.Tensor], weight: torch.Tensor,
+                  bias: Optional[torch.Tensor], eps: float, out: torch.Tensor,
+                  rows: Optional[torch.Tensor] = None) -> None:
+    """residual (+= pending); out = (residual - mean) / sqrt(var + eps) * weight + bias.
+    With `rows` only those rows are read (nothing is written back)."""
+    H = residual.shape[1]
+    R = rows.numel() if rows is not None else residual.shape[0]
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_layernorm: residual must be contiguous float32")
+    for name, t in (("weight", weight), ("bias", bias)):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == H),
+              f"add_layernorm: {name} must be float32 [H]")
+    _need(weight is not None, "add_layernorm: a weight is needed")
+    _need(out.is_contiguous() and tuple(out.shape) == (R, H), "add_layernorm: out must be contiguous [rows, H]")
+    if pending is not None:
+        _need(pending.dtype == out.dtype and pending.is_contiguous() and pending.shape == residual.shape,
+              "add_layernorm: pending must match the residual's shape and out's dtype")
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.is_contiguous(), "add_layernorm: rows must be contiguous int32")
+    _check(_fn("gtg_add_layernorm")(_dt(out), _ptr(residual), _ptr(pending), _ptr(weight), _ptr(bias), float(eps),
+                                    _ptr(out), _ptr(rows), R, H, _stream()), "add_layernorm")
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, kind: str) -> None:
+    """x <- f(x) in place, evaluated in float: "relu2" (relu squared), "gelu_tanh", "silu"."""
+    _rows2d(x, "activation: x")
+    _need(kind in ACTIVATIONS, f"activation: {kind!r} is not known; known: {sorted(ACTIVATIONS)}")
+    _check(_fn("gtg_activation")(_dt(x), _ptr(x), x.stride(0), x.shape[0], x.shape[1], ACTIVATIONS[kind], _stream()),
+           "activation")
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap), in place (float32)."""
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "softcap: logits must be contiguous float32")
+    _need(cap > 0, "softcap: the cap must be positive")
+    _check(_fn("gtg_softcap")(_ptr(logits), logits.numel(), float(cap), _stream()), "softcap")
+
+
+def hidden_concat(residual: torch.Tensor, pending: Optional[torch.Tensor], other: torch.Tensor,
+                  out: torch.Tensor) -> None:
+    """out[:, :H] = residual (+ pending); out[:, H:] = other (float32 [N, H])."""
+    N, H = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and other.dtype == torch.float32
+          and other.is_contiguous() and other.shape == residual.shape,
+          "hidden_concat: residual and other must be contiguous float32 of one shape")
+    _need(out.is_contiguous() and tuple(out.shape) == (N, 2 * H), "hidden_concat: out must be contiguous [N, 2H]")
+    if pending is not None:
+        _need(pending.dtype == out.dtype and pending.is_contiguous() and pending.shape == residual.shape,
+              "hidden_concat: pending must match the residual's shape and out's dtype")
+    _check(_fn("gtg_hidden_concat")(_dt(out), _ptr(residual), _ptr(pending), _ptr(other), _ptr(out), N, H, _stream()),
+           "hidden_concat")
+
+
+# ------------------------------------------------------------- recurrent mixers
+def _int32(name: str, *tensors) -> None:
+    for t in tensors:
+        _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name}: index tensors must be contiguous int32")
+
+
+def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                     conv_state: torch.Tensor, out: torch.Tensor, token_seq, cu_seqlens, slots) -> None:
+    """out[n, c] = silu(bias[c] + sum_j weight[c, j] x[n - (taps-1-j), c]) within each
+    sequence of the packed rows; what precedes a sequence's first row of the step
+    comes from conv_state[slot] ([taps-1, C] float32, oldest first)."""
+    _rows2d(x, "causal_conv_silu: x"); _rows2d(out, "causal_conv_silu: out")
+    n, C = x.shape
+    taps = weight.shape[1]
+    _need(out.dtype == x.dtype and tuple(out.shape) == (n, C), "causal_conv_silu: out must match x")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == C,
+          "causal_conv_silu: weight must be float32 [C, taps]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C),
+          "causal_conv_silu: bias must be float32 [C]")
+    _need(conv_state.dtype == torch.float32 and conv_state.is_contiguous()
+          and tuple(conv_state.shape[1:]) == (taps - 1, C), "causal_conv_silu: conv_state must be float32 [slots, taps-1, C]")
+    _int32("causal_conv_silu", token_seq, cu_seqlens, slots)
+    _check(_fn("gtg_causal_conv_silu")(_dt(x), _ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(conv_state),
+                                       _ptr(out), out.stride(0), _ptr(token_seq), _ptr(cu_seqlens), _ptr(slots),
+                                       n, C, taps, _stream()), "causal_conv_silu")
+
+
+def conv_state_update(x: torch.Tensor, conv_state: torch.Tensor, cu_seqlens, slots, n_seqs: int) -> None:
+    """conv_state[slot] <- the last taps-1 inputs of each sequence, this step's rows included."""
+    _rows2d(x, "conv_state_update: x")
+    C = x.shape[1]
+    keep = conv_state.shape[1]
+    _need(conv_state.dtype == torch.float32 and conv_state.is_contiguous() and conv_state.shape[2] == C,
+          "conv_state_update: conv_state must be float32 [slots, taps-1, C]")
+    _int32("conv_state_update", cu_seqlens, slots)
+    _check(_fn("gtg_conv_state_update")(_dt(x), _ptr(x), x.stride(0), _ptr(conv_state), _ptr(cu_seqlens), _ptr(slots),
+                                        int(n_seqs), C, keep + 1, _stream()), "conv_state_update")
+
+
+def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+             skip: torch.Tensor, state: torch.Tensor, y: torch.Tensor, cu_seqlens, slots, n_seqs: int,
+             heads: int, groups: int, n_state: int, head_dim: int) -> None:
+    """The state-space recurrence with a scalar decay per head, token by token:
+    xbc [n, heads*P + 2*groups*N] = [x | B | C] per row, dt_raw [n, heads];
+    dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T,
+    y = S^T C + skip * x.  state: float32 [slots, heads, N, P], read and left
+    per sequence; y: float32 [n, heads*P]."""
+    _rows2d(xbc, "ssm_scan: xbc"); _rows2d(dt_raw, "ssm_scan: dt_raw"); _rows2d(y, "ssm_scan: y")
+    n = xbc.shape[0]
+    inner = heads * head_dim
+    _need(xbc.shape[1] == inner + 2 * groups * n_state and dt_raw.dtype == xbc.dtype and tuple(dt_raw.shape) == (n, heads),
+          "ssm_scan: xbc must be [n, heads*P + 2*groups*N] and dt_raw [n, heads] of one dtype")
+    _need(y.dtype == torch.float32 and tuple(y.shape) == (n, inner), "ssm_scan: y must be float32 [n, heads*P]")
+    for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("skip", skip)):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == heads, f"ssm_scan: {name} must be float32 [heads]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, n_state, head_dim),
+          "ssm_scan: state must be float32 [slots, heads, N, P]")
+    _int32("ssm_scan", cu_seqlens, slots)
+    _check(_fn("gtg_ssm_scan")(_dt(xbc), _ptr(xbc), xbc.stride(0), _ptr(dt_raw), dt_raw.stride(0), _ptr(dt_bias),
+                               _ptr(a_log), _ptr(skip), _ptr(state), _ptr(y), y.stride(0), _ptr(cu_seqlens), _ptr(slots),
+                               int(n_seqs), heads, groups, n_state, head_dim, _stream()), "ssm_scan")
+
+
+def gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                  parts: int = 1) -> None:
+    """out = rmsnorm_parts(y * silu(z)) * weight: the row is cut into `parts` equal
+    pieces, each divided by its own root mean square.  y float32; z, out the
+    activation dtype."""
+    _rows2d(y, "gated_rmsnorm: y"); _rows2d(z, "gated_rmsnorm: z"); _rows2d(out, "gated_rmsnorm: out")
+    n, width = y.shape
+    _need(y.dtype == torch.float32 and z.dtype == out.dtype and tuple(z.shape) == (n, width) and tuple(out.shape) == (n, width),
+          "gated_rmsnorm: y float32, z and out of one dtype, all [n, width]")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == width,
+          "gated_rmsnorm: weight must be float32 [width]")
+    _need(parts >= 1 and width % parts == 0, f"gated_rmsnorm: {parts} pieces do not divide a row of {width}")
+    _check(_fn("gtg_gated_rmsnorm")(_dt(out), _ptr(y), y.stride(0), _ptr(z), z.stride(0), _ptr(weight), float(eps),
+                                    _ptr(out), out.stride(0), n, width, int(parts), _stream()), "gated_rmsnorm")
 
 
 # ---------------------------------------------------------------- matrix products
@@ -359,6 +507,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
         return
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear: operands must both be bfloat16 or both float32")
     _need(out.dtype in (torch.bfloat16, torch.float32), "linear: out must be bfloat16 or float32")
+    if kind == "auto" and epilogue == "none" and not (
+            K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+            and out.stride(0) % (4 if out.dtype == torch.float32 else 8) == 0):
+        # a shape the tensor-core products cannot address: the plain walk, float accumulation
+        _check(_fn("gtg_gemm_bf16_simt")(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
+                                         1 if out.dtype == torch.float32 else 0, M, N, K, _stream()),
+               "linear(bfloat16, plain)")
+        return
     _need(K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0,
           f"linear(bfloat16): the inner size {K} and the row strides must be multiples of 8")
     # few rows (a decode step): stream the weights once; many rows: tiled product

@@ -9,9 +9,12 @@ rotation, :1253-1254 cache write, :1603-1661 attention, :1290-1297 output).
 Parameters: ``hidden_size``, ``n_heads``, ``n_kv_heads``, ``head_dim``,
 ``window`` (None: all keys), ``scale`` (None: head_dim^-1/2), ``position`` (a
 position PartSpec), ``own_kv`` (False for a layer that has no key/value
-projections and reads another run's cache), and the tensor names ``q``, ``k``,
-``v``, ``o``.  The three projections are fused at load into one matrix
-[(n_heads + 2 n_kv_heads) * head_dim, hidden] so that one product serves them.
+projections and reads another run's cache), ``values`` ("projection", the
+default, or "keys": there is no value projection and the value of a token is
+its key as projected, before the rotation), and the tensor names ``q``, ``k``,
+``v``, ``o``.  The projections are fused at load into one matrix
+[(n_heads + 2 n_kv_heads) * head_dim, hidden] (without the value rows when the
+values are the keys) so that one product serves them.
 """
 from __future__ import annotations
 
@@ -41,8 +44,13 @@ class GQAttention(Mixer):
         scale = self.p.get("scale")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.own_kv = bool(self.p.get("own_kv", True))
+        self.values = str(self.p.get("values") or "projection")
+        if self.values not in ("projection", "keys"):
+            raise ValueError(f"attention values {self.values!r} are not known: 'projection' or 'keys'")
+        self.v_from_k = self.values == "keys"
         self.position = build_part("position", self.param("position"))
-        self.names = {k: str(self.param(k)) for k in (("q", "k", "v", "o") if self.own_kv else ("q", "o"))}
+        wanted = ("q", "o") if not self.own_kv else ("q", "k", "o") if self.v_from_k else ("q", "k", "v", "o")
+        self.names = {k: str(self.param(k)) for k in wanted}
         self.q_dim = self.n_heads * self.head_dim
         self.kv_dim = self.n_kv * self.head_dim
         self.w_qkv: Optional[torch.Tensor] = None
@@ -51,8 +59,9 @@ class GQAttention(Mixer):
     def weight_specs(self) -> List[WeightSpec]:
         specs = [WeightSpec(self.names["q"], (self.q_dim, self.hidden))]
         if self.own_kv:
-            specs += [WeightSpec(self.names["k"], (self.kv_dim, self.hidden)),
-                      WeightSpec(self.names["v"], (self.kv_dim, self.hidden))]
+            specs.append(WeightSpec(self.names["k"], (self.kv_dim, self.hidden)))
+            if not self.v_from_k:
+                specs.append(WeightSpec(self.names["v"], (self.kv_dim, self.hidden)))
         specs.append(WeightSpec(self.names["o"], (self.hidden, self.q_dim)))
         return specs
 
@@ -65,7 +74,9 @@ class GQAttention(Mixer):
     def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
         parts = [tensors[self.names["q"]]]
         if self.own_kv:
-            parts += [tensors[self.names["k"]], tensors[self.names["v"]]]
+            parts.append(tensors[self.names["k"]])
+            if not self.v_from_k:
+                parts.append(tensors[self.names["v"]])
         self.w_qkv = rt.matrix(torch.cat([p.to(rt.dtype) for p in parts], dim=0))
         self.w_o = rt.matrix(tensors[self.names["o"]])
 
@@ -86,7 +97,7 @@ class GQAttention(Mixer):
         # token's key and value itself, and no kernel stands between it and the projection
         in_attention = (ctx.is_decode and rt.dtype == torch.bfloat16 and plain_layout
                         and ops.attention_bf16_supports(self.head_dim))
-        if store and plain_layout and ops.qkv_rope_fused_supports(x, self.w_qkv, qkv, rotation, self.n_heads,
+        if store and plain_layout and not self.v_from_k and ops.qkv_rope_fused_supports(x, self.w_qkv, qkv, rotation, self.n_heads,
                                                                   self.n_kv, self.head_dim, kv):
             # a prompt: rotation and cache store happen in the projection's epilogue
             ops.linear_qkv_rope(x, self.w_qkv, qkv, rotation, self.n_heads, self.n_kv, kv,
@@ -98,11 +109,11 @@ class GQAttention(Mixer):
                 ctx.trace("q", qkv[:, : self.q_dim].clone())
                 if self.own_kv:
                     ctx.trace("k", qkv[:, self.q_dim: self.q_dim + self.kv_dim])
-                    ctx.trace("v", qkv[:, self.q_dim + self.kv_dim:])
+                    ctx.trace("v", qkv[:, self.q_dim + (0 if self.v_from_k else self.kv_dim):][:, : self.kv_dim])
             if not in_attention:
                 ops.rope_kv_store(qkv, rotation, self.n_heads, store, self.head_dim,
                                   kv, ctx.token_seq, ctx.slots, ctx.positions,
-                                  pairing=pairing, rotary_dim=rotary_dim)
+                                  pairing=pairing, rotary_dim=rotary_dim, values_from_keys=self.v_from_k)
         q = qkv[:, : self.q_dim]
         if not in_attention:
             ctx.trace("q_attn", q)
@@ -111,7 +122,7 @@ class GQAttention(Mixer):
         if rt.dtype == torch.bfloat16 and ops.attention_bf16_supports(self.head_dim):
             if ctx.is_decode:
                 new_k = qkv[:, self.q_dim: self.q_dim + self.kv_dim] if store else None
-                new_v = qkv[:, self.q_dim + self.kv_dim:] if store else None
+                new_v = (new_k if self.v_from_k else qkv[:, self.q_dim + self.kv_dim:]) if store else None
                 splits, chunk, ring = ops.attention_decode_plan(n, self.n_heads, self.n_kv, self.head_dim,
                                                           ctx.max_kv_len, window, ctx.total_kv_len)
                 scratch = None

@@ -336,14 +336,19 @@ class Block(Part):
     plan, for the parts of a layer, their tensors and their cache needs.  A
     block may declare tensors of its own too (`weight_specs`, `load`)."""
     sub_parts: Tuple[Tuple[str, str], ...] = ()
+    # names among `sub_parts` whose spec may be None: the attribute is then None
+    optional_parts: Tuple[str, ...] = ()
 
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
         for name, category in self.sub_parts:
-            setattr(self, name, build_part(category, self.param(name)))
+            if name in self.optional_parts and self.p.get(name) is None:
+                setattr(self, name, None)
+            else:
+                setattr(self, name, build_part(category, self.param(name)))
 
     def children(self) -> List[Part]:
-        return [getattr(self, name) for name, _ in self.sub_parts]
+        return [part for part in (getattr(self, name) for name, _ in self.sub_parts) if part is not None]
 
     def cache_requests(self) -> List[Request]:
         """What one run of this layer keeps per sequence: what its parts ask for."""

@@ -3,13 +3,16 @@
 ``token_embedding``: x = E[token], unscaled (model/inference_helpers.go:9-34);
 it starts the float32 residual stream.  Parameters: ``vocab_size``,
 ``hidden_size``, ``weight`` and optionally ``position`` (a position PartSpec
-whose `on_embedding` hook acts on the embedded tokens).
+whose `on_embedding` hook acts on the embedded tokens) and ``keep_output``
+(True: a float32 copy of the embedded tokens stays in the step's shared values
+as "embedding_output" for later parts to read).
 
 ``lm_head``: logits = x . LM^T in float32 for the rows it is given
 (model/inference_helpers.go:122-148).  ``weight`` names the table; with
 ``tied`` it is the embedding's tensor and one device copy serves both
 (model/llama.go:490-494 decides tying by the tensor's presence; here the
 configuration's flag decides and a stray ``ignored`` tensor is tolerated).
+With ``softcap`` c the logits become c * tanh(logits / c).
 """
 from __future__ import annotations
 
@@ -32,6 +35,7 @@ class TokenEmbedding(Embedding):
         self.weight_name = str(self.param("weight"))
         pos = self.p.get("position")
         self.position = build_part("position", pos) if pos is not None else None
+        self.keep_output = bool(self.p.get("keep_output", False))
         self.table: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -46,6 +50,10 @@ class TokenEmbedding(Embedding):
     def forward(self, ctx: StepContext) -> ResidualStream:
         residual = ctx.rt.empty(ctx.n_tokens, self.hidden, dtype=torch.float32, lifetime="step")
         ops.embed(ctx.tokens, self.table, residual)
+        if self.keep_output:
+            kept = ctx.rt.empty(ctx.n_tokens, self.hidden, dtype=torch.float32, lifetime="step")
+            ops.embed(ctx.tokens, self.table, kept)
+            ctx.shared["embedding_output"] = kept
         stream = ResidualStream(residual)
         if self.position:
             self.position.on_embedding(stream, ctx)
@@ -61,6 +69,8 @@ class LMHead(Head):
         self.weight_name = str(self.param("weight"))
         self.tied = bool(self.p.get("tied", False))
         self.ignored = self.p.get("ignored")
+        cap = self.p.get("softcap")
+        self.softcap = float(cap) if cap else None
         self.table: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -76,4 +86,6 @@ class LMHead(Head):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         logits = ctx.rt.result(x.shape[0], self.vocab, dtype=torch.float32)
         ops.linear(x, self.table, logits)
+        if self.softcap:
+            ops.softcap(logits, self.softcap)
         return logits

@@ -1,4 +1,11 @@
-"""Dense gated feed-forward (SwiGLU): down(silu(gate(x)) * up(x)), silu(g) =
+"""Feed-forwards.
+
+``dense``: down(act(up(x))) without a gate; ``activation`` is "relu2" (the
+square of relu), "gelu_tanh" or "silu", applied in float.  Parameters:
+``hidden_size``, ``intermediate_size``, ``activation`` and the tensor names
+``up``, ``down``.  The reference has no ungated feed-forward.
+
+``swiglu``: dense gated feed-forward (SwiGLU): down(silu(gate(x)) * up(x)), silu(g) =
 g / (1 + exp(-g)) (model/llama.go:1361-1401, backends/simd/vec.go:52-59).
 
 Parameters: ``hidden_size``, ``intermediate_size`` and the tensor names
@@ -58,5 +65,37 @@ class SwiGLU(FeedForward):
             ctx.trace("gate_pre", gate_up[:, : self.inter])
             ctx.trace("up", gate_up[:, self.inter:])
             ops.swiglu(gate_up, act)
+        ctx.trace("gate_act", act)
+        return emit_update(act, self.w_down, ctx)
+
+
+@register_part("feed_forward", "dense")
+class DenseFeedForward(FeedForward):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.param("hidden_size"))
+        self.inter = int(self.param("intermediate_size"))
+        self.activation = str(self.p.get("activation") or "relu2")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"feed-forward activation {self.activation!r} is not known; known: {sorted(ops.ACTIVATIONS)}")
+        self.names = {k: str(self.param(k)) for k in ("up", "down")}
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.names["up"], (self.inter, self.hidden)),
+                WeightSpec(self.names["down"], (self.hidden, self.inter))]
+
+    def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        self.w_up = rt.matrix(tensors[self.names["up"]])
+        self.w_down = rt.matrix(tensors[self.names["down"]])
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        rt = ctx.rt
+        n = x.shape[0]
+        act = rt.empty(n, (self.inter + 7) // 8 * 8)[:, : self.inter]
+        ops.linear(x, self.w_up, act)
+        ctx.trace("up", lambda: act.clone())
+        ops.activation(act, self.activation)
         ctx.trace("gate_act", act)
         return emit_update(act, self.w_down, ctx)

@@ -19,6 +19,15 @@ original/high_freq_factor keep their frequency, longer than
 original/low_freq_factor are divided by `factor`, and those in between are
 blended linearly.
 
+The yarn scaling (``scaling`` = {"rope_type": "yarn", factor, original, fast,
+slow}; not in the reference either) blends by the pair's index instead: pair
+i turns original * f_i / (2 pi) times within `original` positions; between
+the pair that turns `fast` times (index lo, rounded down) and the one that
+turns `slow` times (index hi, rounded up) a linear ramp r_i goes from 0 to 1,
+and the frequency is f_i (1 - r_i) + f_i / factor * r_i.  Cosines and sines
+are multiplied by 0.1 ln(factor) + 1, which sharpens the attention as the
+context is stretched.
+
 ``none``: no position encoding.
 """
 from __future__ import annotations
@@ -32,9 +41,31 @@ from ..kernels import ops
 from .base import PositionEncoding, Runtime, StepContext, register_part
 
 
+def yarn_ramp(rotary_dim: int, theta: float, original: float, fast: float, slow: float):
+    """r_i for every pair: 0 up to the pair that turns `fast` times within
+    `original` positions, 1 from the pair that turns `slow` times."""
+    def pair_that_turns(turns: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+    lo = max(math.floor(pair_that_turns(fast)), 0)
+    hi = min(math.ceil(pair_that_turns(slow)), rotary_dim - 1)
+    width = max(hi - lo, 0.001)
+    return [min(max((i - lo) / width, 0.0), 1.0) for i in range(rotary_dim // 2)]
+
+
+def rotary_amplitude(scaling: Optional[Mapping] = None) -> float:
+    """What cosines and sines are multiplied by: 1, or 0.1 ln(factor) + 1 under yarn."""
+    if scaling and scaling.get("rope_type") == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
+
+
 def rotary_frequencies(head_dim: int, theta: float, scaling: Optional[Mapping] = None):
     """float64 list of head_dim/2 frequencies."""
     freqs = [1.0 / math.pow(theta, (2 * i) / head_dim) for i in range(head_dim // 2)]
+    if scaling and scaling.get("rope_type") == "yarn":
+        factor = float(scaling["factor"])
+        ramp = yarn_ramp(head_dim, theta, float(scaling["original"]), float(scaling["fast"]), float(scaling["slow"]))
+        return [f / factor * r + f * (1.0 - r) for f, r in zip(freqs, ramp)]
     if scaling:
         factor = float(scaling["factor"])
         low = float(scaling["low_freq_factor"])
@@ -71,6 +102,7 @@ class RotaryEncoding(PositionEncoding):
                              f"{self.head_dim}, got {self.rotary_dim}")
         self._key = ("rotary", self.rotary_dim, self.theta,
                      tuple(sorted(self.scaling.items())) if self.scaling else None)
+        self.amplitude = rotary_amplitude(self.scaling)
         self.inv_freq: Optional[torch.Tensor] = None
 
     def load(self, tensors, rt: Runtime) -> None:
@@ -81,7 +113,7 @@ class RotaryEncoding(PositionEncoding):
         table = ctx.shared.get(self._key)
         if table is None:
             table = ctx.rt.empty(ctx.n_tokens, self.rotary_dim // 2, 2, dtype=torch.float32, lifetime="step")
-            ops.rope_table(ctx.positions, self.inv_freq, table)
+            ops.rope_table(ctx.positions, self.inv_freq, table, self.amplitude)
             ctx.shared[self._key] = table
         return table
 

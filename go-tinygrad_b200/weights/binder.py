@@ -24,9 +24,11 @@ class WeightSpec:
     name: str
     shape: Tuple[int, ...]
     # 'matrix' and 'table' follow the run's compute dtype; 'vector' (norm scales
-    # and the like) is always held in float32; 'ignored' may be in the file but
-    # is never read.  'std' and 'mean' are what the
-    # random-weights mode draws from.
+    # and the like) is always held in float32; 'parameter' too (small tensors of
+    # a recurrence or a convolution), but the random-weights mode draws it from
+    # the spec's own 'std' and 'mean' whatever the caller asks for matrices and
+    # norms; 'ignored' may be in the file but is never read.  'std' and 'mean'
+    # are what the random-weights mode draws from.
     role: str = "matrix"
     optional: bool = False
     std: float = 0.02
