@@ -27,6 +27,12 @@ at a context of 8192 tokens.  It prints ONE JSON line:
   cpu_baseline  for context only: the plain NumPy implementation of tests/ on the
              host, tiny-llama-A, tokens a second
 
+With --design ropovik it measures the Ropovik design instead (see `run_design`):
+prefill and decode of a looped stack of Mamba-2 and attention layers at the
+layer sizes of two real models, beside the Llama decoder at equal width, depth
+and heads, and every kernel the design added beside the like kernel of the
+Llama path, each against the copy peak.  The default run is not changed by it.
+
 Peaks come from MEASURED_PEAKS.json beside this file if present, else from the
 fallback figures of an earlier measurement on the same pool.  Inputs are larger
 than L2 (3.4 GB of weights and 1.6 GB of cache per sequence against 126 MB), so
@@ -444,6 +450,183 @@ def run_own(args):
     return 0
 
 
+
+# ------------------------------------------------------------------ --design ropovik
+def ropovik_shape(width, heads, kv_heads, dim, ff, m_heads, m_dim, m_state, m_groups, vocab=32000):
+    """Four layers (recurrence, attention, recurrence, attention, each with a dense
+    feed-forward) that run twice: eight layer runs and two loop projections."""
+    attn = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                      "rot": {"dims": dim, "base": 10000.0,
+                              "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+    mamba = {"type": "mamba2", "mlp": {"kind": "dense", "ff": ff},
+             "mixer": {"heads": m_heads, "vdim": m_dim, "state": m_state, "groups": m_groups, "conv": 4,
+                       "norm_groups": m_groups}}
+    return {"architecture": "Ropovik", "vocab": vocab, "width": width, "logit_softcap": 30.0, "norm": {"eps": 1e-5},
+            "loop": {"start": 0, "stop": 4, "times": 2}, "layers": [mamba, attn, mamba, attn]}
+
+
+DESIGN_SIZES = {
+    # the layer sizes of Llama-3.2-1B / SmolLM2 (width 2048) and of Llama-3.1-8B (width 4096); the
+    # recurrence has twice the width in its inner size, heads of 64 and a state of 128, as Mamba-2 models do
+    "w2048": (ropovik_shape(2048, 32, 8, 64, 8192, 64, 64, 128, 8), dict(LLAMA_3P2_1B, num_hidden_layers=8, vocab_size=32000)),
+    "w4096": (ropovik_shape(4096, 32, 8, 128, 14336, 128, 64, 128, 8), dict(LLAMA_3P1_8B, num_hidden_layers=8, vocab_size=32000)),
+}
+
+
+def run_design(args):
+    """Prefill and decode throughput of the Ropovik design beside the Llama decoder at
+    equal width, depth and heads (random weights, bfloat16), and its own kernels one
+    by one against the copy peak beside the like kernel of the Llama path.  One JSON line."""
+    import torch
+    import go_tinygrad_b200 as lib
+    from go_tinygrad_b200.engine import StepEntry, step
+    from go_tinygrad_b200.engine.decode import DecodeBatch
+    from go_tinygrad_b200.kernels import ops
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    gen = torch.Generator().manual_seed(0)
+    T, prompt_len = 2048, 1024
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the L2
+
+    def timed(fn, repeats=10, warm=3):
+        """Median device time of fn() in ms, the L2 flushed before every call."""
+        times = []
+        for i in range(warm + repeats):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                times.append(a.elapsed_time(b))
+        return statistics.median(times)
+
+    def model_numbers(cfg):
+        model = lib.Model.random(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02)
+        vocab = model.plan.vocab_size
+        cache = model.new_cache(max_tokens=64 * (prompt_len + 256) + T + 64, max_slots=65)
+        out = {}
+        prompt = torch.randint(0, vocab, (T,), generator=gen).numpy()
+
+        def prefill():
+            slot = cache.open_sequence()
+            step(model, cache, [StepEntry(slot, prompt, [T - 1])])
+            cache.close_sequence(slot)
+        ms = timed(prefill, repeats=5)
+        out["prefill_2048"] = {"ms": round(ms, 3), "tokens_per_s": round(T / ms * 1e3, 1)}
+        for batch in (8, 64):
+            slots = [cache.open_sequence() for _ in range(batch)]
+            prompts = [torch.randint(0, vocab, (prompt_len,), generator=gen).numpy() for _ in range(batch)]
+            tokens = []
+            for lo in range(0, batch, 8):
+                logits = step(model, cache, [StepEntry(s, p, [prompt_len - 1]) for s, p in zip(slots[lo:lo + 8], prompts[lo:lo + 8])])
+                tokens += logits.argmax(dim=1).tolist()
+            steps, warm = args.steps, max(args.warmup, 10)
+            for s in slots:
+                cache.reserve(s, prompt_len + steps + warm + 2)
+            cache.flush_tables()
+            db = DecodeBatch(model, cache, slots, list(range(batch)), lib.Sampler(0.0, 0))
+            db.set_state(tokens, [0] * batch)
+            before = ops.launch_count()
+            db._launch()
+            launches = ops.launch_count() - before + 1
+            for _ in range(warm):
+                db.step_device()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                db.step_device()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / steps
+            out[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3, 1),
+                                       "context": prompt_len, "launches_per_step": launches}
+            for s in slots:
+                cache.close_sequence(s)
+        out["weight_gb"] = round(model.weight_bytes() / 1e9, 3)
+        del model, cache
+        torch.cuda.empty_cache()
+        return out
+
+    def kernel_table(cfg):
+        """Each kernel the design added, alone, at this size: a prompt of T tokens and a
+        decode step of 64 sequences; bytes it has to move / time / the copy peak.  Beside
+        each the like kernel of the Llama path at the same rows."""
+        bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+        m = cfg["layers"][0]["mixer"]
+        at = cfg["layers"][1]["mixer"]
+        H, heads, P, N, G, taps = cfg["width"], m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
+        inner, conv_dim = heads * P, heads * P + 2 * G * N
+        ff = cfg["layers"][0]["mlp"]["ff"]
+        rows = []
+
+        def add(name, rows_n, ms, nbytes, like=None):
+            rows.append({"kernel": name, "rows": rows_n, "us": round(ms * 1e3, 2), "mb": round(nbytes / 1e6, 2),
+                         "gbs": round(nbytes / ms / 1e6, 1), "of_copy_peak": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3),
+                         **({"like": like} if like else {})})
+        rnd = lambda *shape, dtype=bf: torch.randn(*shape, device=dev, dtype=f32).to(dtype)
+        for n, n_seqs, tag in ((T, 1, "prompt"), (64, 64, "decode")):
+            per = n // n_seqs
+            cu = torch.arange(0, n + 1, per, dtype=i32, device=dev)
+            seq = torch.arange(n, dtype=i32, device=dev) // per
+            slots = torch.arange(n_seqs, dtype=i32, device=dev)
+            one = per == 1
+            # norms
+            res, pend, w, b = rnd(n, H, dtype=f32), rnd(n, H), rnd(H, dtype=f32), rnd(H, dtype=f32)
+            out = torch.empty(n, H, dtype=bf, device=dev)
+            add(f"add_layernorm ({tag})", n, timed(lambda: ops.add_layernorm(res, pend, w, b, 1e-5, out)), n * H * (4 + 4 + 2 + 2))
+            add(f"add_rmsnorm ({tag})", n, timed(lambda: ops.add_rmsnorm(res, pend, w, 1e-5, out)), n * H * (4 + 4 + 2 + 2), like="add_layernorm")
+            # activation beside the unfused gate of the Llama path
+            act, gate_up, half = rnd(n, ff), rnd(n, 2 * ff), torch.empty(n, ff, dtype=bf, device=dev)
+            add(f"activation relu2 ({tag})", n, timed(lambda: ops.activation(act, "relu2")), n * ff * 4)
+            add(f"swiglu ({tag})", n, timed(lambda: ops.swiglu(gate_up, half)), n * ff * 6, like="activation")
+            # the hidden state beside the embedding output
+            other, both = rnd(n, H, dtype=f32), torch.empty(n, 2 * H, dtype=bf, device=dev)
+            add(f"hidden_concat ({tag})", n, timed(lambda: ops.hidden_concat(res, pend, other, both)), n * H * (4 + 2 + 4 + 4))
+            # convolution and recurrence
+            proj = rnd(n, inner + conv_dim + heads)
+            conv_in, z, dt_raw = proj[:, inner:inner + conv_dim], proj[:, :inner], proj[:, inner + conv_dim:]
+            cw, cb = rnd(taps, conv_dim, dtype=f32), rnd(conv_dim, dtype=f32)
+            cstate = torch.zeros(n_seqs, taps - 1, conv_dim, device=dev)
+            xbc = torch.empty(n, conv_dim, dtype=bf, device=dev)
+            add(f"causal_conv_silu + state ({tag})", n,
+                timed(lambda: ops.causal_conv_silu(conv_in, cw, cb, cstate, xbc, seq, cu, slots, n_seqs=n_seqs,
+                                                   update_state=True, one_token_each=one)),
+                n * conv_dim * 4 + (2 * n_seqs * (taps - 1) * conv_dim * 4 if one else 0))
+            dtb, al, sk = rnd(heads, dtype=f32) - 2.0, rnd(heads, dtype=f32), rnd(heads, dtype=f32)
+            sstate = torch.zeros(n_seqs, heads, N, P, device=dev)
+            y = torch.empty(n, inner, dtype=f32, device=dev)
+            scan_bytes = n * (conv_dim * 2 + inner * 4) + 2 * n_seqs * heads * N * P * 4
+            add(f"ssm_scan ({tag})", n,
+                timed(lambda: ops.ssm_scan(xbc, dt_raw, dtb, al, sk, sstate, y, cu, slots, n_seqs, heads, G, N, P,
+                                           one_token_each=one)), scan_bytes)
+            gated, norm_w = torch.empty(n, inner, dtype=bf, device=dev), torch.ones(inner, device=dev)
+            add(f"gated_rmsnorm ({tag})", n, timed(lambda: ops.gated_rmsnorm(y, z, norm_w, 1e-5, gated, G)),
+                n * inner * (4 + 2 + 2))
+        return rows
+
+    sampler = ClockSampler()
+    sampler.start()
+    sampler.mark()
+    sizes = {}
+    for name in (args.sizes.split(",") if args.sizes else list(DESIGN_SIZES)):
+        ropovik_cfg, llama_cfg = DESIGN_SIZES[name]
+        sizes[name] = {"ropovik": model_numbers(ropovik_cfg), "llama": model_numbers(llama_cfg),
+                       "kernels": kernel_table(ropovik_cfg)}
+    clocks = sampler.stop()
+    print(json.dumps({"design": "ropovik", "dtype": "bf16", "data": "synthetic (random weights and token ids)",
+                      "what": "4 layers (mamba2, attention, mamba2, attention, a dense feed-forward each) run twice, "
+                              "beside 8 Llama layers of equal width, heads and feed-forward size; vocabulary 32000",
+                      "peaks": pk, "l2": "flushed before every timed prefill and kernel; decode steps read more than the L2 holds",
+                      "steps": args.steps, "clocks": clocks, "sizes": sizes}))
+    return 0
+
+
 def cpu_baseline():
     """For context only: the plain NumPy implementation that the tests use as their
     oracle, on the host, at tiny-llama-A (three prompts of 5, 17 and 32 tokens, 16
@@ -497,6 +680,9 @@ def main():
                     help="with --only: also print, as comment lines, the time each kernel adds to a step")
     ap.add_argument("--eager", action="store_true",
                     help="launch the decode step kernel by kernel instead of replaying a graph")
+    ap.add_argument("--design", default=None, choices=["ropovik"],
+                    help="measure this design beside the Llama decoder at equal size instead of the default workload")
+    ap.add_argument("--sizes", default="", help="with --design: which of its sizes, comma separated (default: all)")
     ap.add_argument("--no-chain", action="store_true",
                     help="decode kernels wait for their predecessor to finish before they are launched")
     args = ap.parse_args()
@@ -511,6 +697,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design:
+        return run_design(args)
     return run_own(args)
 
 

@@ -475,10 +475,78 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const T* __re
         o[i] = from_f32<T>((row[i] - mean) * s * weight[i] + (bias ? bias[i] : 0.f));
 }
 
+// The same for bfloat16 rows whose width is a multiple of 8 and at most 8192:
+// every thread owns 8 consecutive channels, kept in registers through both passes.
+__global__ void __launch_bounds__(1024)
+add_layernorm_bf16_vec_kernel(float* __restrict__ residual, const bf16* __restrict__ pending,
+                              const float* __restrict__ weight, const float* __restrict__ bias, float eps,
+                              bf16* __restrict__ out, const int* __restrict__ rows, int H) {
+    chain_release();
+    chain_wait();
+    __shared__ float scratch[33];
+    const int i_out = blockIdx.x;
+    const int r = rows ? rows[i_out] : i_out;
+    const int c = threadIdx.x * 8;
+    const bool active = c < H;
+    float x[8];
+    float sum = 0.f;
+    if (active) {
+        float4* rp = reinterpret_cast<float4*>(residual + (size_t)r * H + c);
+        const float4 a = rp[0], b = rp[1];
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+        if (pending) {
+            const uint4 p = *reinterpret_cast<const uint4*>(pending + (size_t)r * H + c);
+            const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&p);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(ph[j]);
+                x[2 * j] += f.x;
+                x[2 * j + 1] += f.y;
+            }
+            if (!rows) {
+                rp[0] = make_float4(x[0], x[1], x[2], x[3]);
+                rp[1] = make_float4(x[4], x[5], x[6], x[7]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum += x[j];
+    }
+    const float mean = block_sum(sum, scratch) / (float)H;
+    float ss = 0.f;
+    if (active) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { x[j] -= mean; ss += x[j] * x[j]; }
+    }
+    const float var = block_sum(ss, scratch) / (float)H;
+    const float s = 1.0f / sqrtf(var + eps);
+    if (active) {
+        const float4* wp = reinterpret_cast<const float4*>(weight + c);
+        const float4 w0 = wp[0], w1 = wp[1];
+        const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        float bb[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (bias) {
+            const float4* bp = reinterpret_cast<const float4*>(bias + c);
+            const float4 b0 = bp[0], b1 = bp[1];
+            bb[0] = b0.x; bb[1] = b0.y; bb[2] = b0.z; bb[3] = b0.w; bb[4] = b1.x; bb[5] = b1.y; bb[6] = b1.z; bb[7] = b1.w;
+        }
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            oh[j] = __floats2bfloat162_rn(x[2 * j] * s * w[2 * j] + bb[2 * j], x[2 * j + 1] * s * w[2 * j + 1] + bb[2 * j + 1]);
+        *reinterpret_cast<uint4*>(out + (size_t)i_out * H + c) = o;
+    }
+}
+
 GTG_API int gtg_add_layernorm(int dtype, float* residual, const void* pending, const float* weight,
                               const float* bias, float eps, void* out, const int* rows, int R, int H,
                               cudaStream_t stream) {
     if (R <= 0) return 0;
+    if (dtype == 1 && H % 8 == 0 && H <= 8192 && ((uintptr_t)residual % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
+        ((uintptr_t)weight % 16) == 0 && ((uintptr_t)bias % 16) == 0 && ((uintptr_t)pending % 16) == 0) {
+        const int t = ((H / 8) + 31) / 32 * 32;
+        return launch_chained(add_layernorm_bf16_vec_kernel, dim3(R), dim3(t), 0, stream, residual, (const bf16*)pending, weight, bias, eps, (bf16*)out, rows, H);
+    }
     int threads = 32;
     while (threads < 1024 && threads * 4 < H) threads *= 2;
     const size_t smem = (size_t)(H + 33) * sizeof(float);

@@ -17,8 +17,9 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x));
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
 // ------------------------------------------------ causal convolution + silu
-// out[n, c] = silu(bias[c] + sum_j w[c, j] * in[n - (taps-1-j), c]): the last tap is
-// the current token's.  Inputs before the first row of the step come from
+// out[n, c] = silu(bias[c] + sum_j w[j, c] * in[n - (taps-1-j), c]): the last tap is
+// the current token's; w is held tap by tap, [taps, C], so that neighbouring
+// channels read neighbouring weights.  Inputs before the first row of the step come from
 // conv_state[slot, taps-1, C] (the sequence's last taps-1 inputs, oldest first;
 // zero for a new sequence).  The sum runs in the same order however the
 // sequence was cut into steps.
@@ -42,9 +43,54 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int ld_in, con
         const int back = keep - j;
         const float v = i - back >= 0 ? to_f32<T>(in[(size_t)(n - back) * ld_in + c])
                                       : st[(size_t)(keep + i - back) * C + c];
-        acc = fmaf(w[(size_t)c * taps + j], v, acc);
+        acc = fmaf(w[(size_t)j * C + c], v, acc);
     }
     out[(size_t)n * ld_out + c] = from_f32<T>(silu_f(acc));
+}
+
+// The same for bfloat16 rows of 16-byte aligned runs: a thread takes 8 neighbouring
+// channels of one token with 16-byte accesses (same sum, same order).
+__global__ void causal_conv_silu_bf16_vec_kernel(const bf16* __restrict__ in, int ld_in, const float* __restrict__ w,
+                                                 const float* __restrict__ bias, const float* __restrict__ conv_state,
+                                                 bf16* __restrict__ out, int ld_out, const int* __restrict__ token_seq,
+                                                 const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                                                 int C, int taps) {
+    chain_release();
+    chain_wait();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= C) return;
+    const int n = blockIdx.x;
+    const int b = token_seq[n];
+    const int i = n - cu_seqlens[b];
+    const int keep = taps - 1;
+    const float* st = conv_state + (size_t)slots[b] * keep * C;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = bias ? bias[c + e] : 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int back = keep - j;
+        float v[8];
+        if (i - back >= 0) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(in + (size_t)(n - back) * ld_in + c);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+        } else {
+            const float4* sp = reinterpret_cast<const float4*>(st + (size_t)(keep + i - back) * C + c);
+            const float4 a = sp[0], d = sp[1];
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = d.x; v[5] = d.y; v[6] = d.z; v[7] = d.w;
+        }
+        const float4* wp = reinterpret_cast<const float4*>(w + (size_t)j * C + c);
+        const float4 w0 = wp[0], w1 = wp[1];
+        const float wj[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(wj[e], v[e], acc[e]);
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(silu_f(acc[2 * e]), silu_f(acc[2 * e + 1]));
+    *reinterpret_cast<uint4*>(out + (size_t)n * ld_out + c) = o;
 }
 
 // After the convolution: the state becomes the last taps-1 inputs of each
@@ -69,91 +115,255 @@ __global__ void conv_state_update_kernel(const T* __restrict__ in, int ld_in, fl
     }
 }
 
+// A step in which every sequence brings one token: convolution and state update
+// in one kernel, one thread per (sequence, channel); the same sum in the same order.
+template <typename T>
+__global__ void causal_conv_step_kernel(const T* __restrict__ in, int ld_in, const float* __restrict__ w,
+                                        const float* __restrict__ bias, float* __restrict__ conv_state,
+                                        T* __restrict__ out, int ld_out, const int* __restrict__ slots,
+                                        int C, int taps) {
+    chain_release();
+    chain_wait();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int b = blockIdx.x;
+    const int keep = taps - 1;
+    float* st = conv_state + (size_t)slots[b] * keep * C;
+    const float cur = to_f32<T>(in[(size_t)b * ld_in + c]);
+    float acc = bias ? bias[c] : 0.f;
+    for (int j = 0; j < keep; ++j) {
+        const float v = st[(size_t)j * C + c];
+        acc = fmaf(w[(size_t)j * C + c], v, acc);
+        if (j > 0) st[(size_t)(j - 1) * C + c] = v;
+    }
+    acc = fmaf(w[(size_t)keep * C + c], cur, acc);
+    if (keep > 0) st[(size_t)(keep - 1) * C + c] = cur;
+    out[(size_t)b * ld_out + c] = from_f32<T>(silu_f(acc));
+}
+
 // ------------------------------------------- the recurrence, token by token
 // Per head h (group g = h / (heads / groups)), with x_t [P], B_t, C_t [N], the
 // step size dt_t = softplus(raw_t + dt_bias[h]) and the decay a_t = exp(-exp(a_log[h]) dt_t):
 //     S_t = a_t S_{t-1} + dt_t B_t x_t^T          (S is N x P, float, kept per sequence)
 //     y_t = S_t^T C_t + D[h] x_t
-// One block per (head, sequence).  Thread (p, r) owns column p of S for the rows
-// n = r, r + R, ...; the R partial sums of y_t[p] meet by shuffles.  Tokens are
-// walked strictly in order, so the result does not depend on the cut of the
-// sequence into steps nor on the batch.  x, B and C of kTile tokens at a time
-// are staged in shared memory.
+// The columns of S never meet, so one block serves (head, sequence, a slice of PS
+// columns): the slices give a single long prompt enough blocks to fill the
+// device.  Thread (p, r) owns column p for the rows n = r, r + R, ...; the R
+// partial sums of y_t[p] meet by shuffles, four tokens' worth at a time so that
+// their latencies overlap.  Tokens are walked strictly in order: the result does
+// not depend on the cut of the sequence into steps, on the batch or on the slices.
+// x, B and C of kTile tokens at a time are staged in shared memory.
 constexpr int kTile = 16;
 constexpr int kRowsPerThread = 16;
 
-template <typename T>
+__device__ __forceinline__ void copy_async_16(void* smem_dst, const void* gmem_src) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void copy_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
+
+// kAsync: the rows of x, B and C are 16-byte aligned runs, fetched two tiles ahead
+// by asynchronous copies into a raw staging area and widened to float from there;
+// otherwise (odd sizes) they are read element by element when their tile begins.
+// KR: rows of S a thread owns (R * KR >= N; the rows beyond N, if any, are skipped).
+template <typename T, bool kAsync, int KR>
 __global__ void ssm_scan_kernel(const T* __restrict__ xbc, int ld_xbc, const T* __restrict__ dt_raw, int ld_dt,
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                 const float* __restrict__ skip, float* __restrict__ state,
                                 float* __restrict__ y, int ld_y, const int* __restrict__ cu_seqlens,
-                                const int* __restrict__ slots, int heads, int groups, int N, int P, int R) {
+                                const int* __restrict__ slots, int heads, int groups, int N, int P, int R, int PS) {
     chain_release();
     chain_wait();
-    extern __shared__ float smem[];
-    float* sx = smem;                        // kTile * P
-    float* sB = sx + kTile * P;              // kTile * N
-    float* sC = sB + kTile * N;              // kTile * N
-    float* sdt = sC + kTile * N;             // kTile
-    float* sa = sdt + kTile;                 // kTile
-    const int h = blockIdx.x, b = blockIdx.y;
+    extern __shared__ __align__(16) float smem[];
+    constexpr int kVec = 16 / (int)sizeof(T);
+    float2* sBC = reinterpret_cast<float2*>(smem);          // kTile * N pairs (B, C)
+    float* sx = smem + 2 * kTile * N;                       // kTile * PS
+    float2* sda = reinterpret_cast<float2*>(sx + kTile * PS);   // kTile pairs (dt, a)
+    // raw staging, two tiles: per token [B: N | C: N | x: PS] of T (kAsync only)
+    T* raw = reinterpret_cast<T*>(sda + kTile);
+    const int raw_row = 2 * N + PS, raw_tile = kTile * raw_row;
+    const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * PS;
+    const int cols = min(PS, P - p0);
     const int g = h / (heads / groups);
     const int inner = heads * P;
     const int tid = threadIdx.x;
-    const int p = tid / R, r = tid - p * R;
-    const bool owner = p < P;
+    const int pl = tid / R, r = tid - pl * R;
+    const bool owner = pl < cols;
+    const int p = p0 + pl;
     const int first = cu_seqlens[b], last = cu_seqlens[b + 1];
     float* S = state + ((size_t)slots[b] * heads + h) * N * P;
-    float s[kRowsPerThread];
+    float s[KR];
 #pragma unroll
-    for (int k = 0; k < kRowsPerThread; ++k) {
+    for (int k = 0; k < KR; ++k) {
         const int n = r + R * k;
         s[k] = (owner && n < N) ? S[(size_t)n * P + p] : 0.f;
     }
     const float bias = dt_bias[h], rate = expf(a_log[h]), d_skip = skip[h];
+    const bool exact = R * KR == N;                          // no row of a thread lies beyond N
 
-    for (int t0 = first; t0 < last; t0 += kTile) {
-        const int nt = min(kTile, last - t0);
-        __syncthreads();
-        for (int idx = tid; idx < nt * P; idx += blockDim.x) {
-            const int tt = idx / P, pp = idx - tt * P;
-            sx[idx] = to_f32<T>(xbc[(size_t)(t0 + tt) * ld_xbc + h * P + pp]);
+    // one tile's rows into raw stage `stage`; always one commit, so that groups count tiles
+    auto fetch = [&](int t0, int stage) {
+        if (t0 < last) {
+            const int nt = min(kTile, last - t0);
+            const int nv = N / kVec, xv = PS / kVec, per_row = 2 * nv + xv;
+            T* dst_tile = raw + stage * raw_tile;
+            for (int v = tid; v < nt * per_row; v += blockDim.x) {
+                const int tt = v / per_row, j = v - tt * per_row;
+                const T* row = xbc + (size_t)(t0 + tt) * ld_xbc;
+                const T* src = j < nv ? row + inner + g * N + j * kVec
+                             : j < 2 * nv ? row + inner + (groups + g) * N + (j - nv) * kVec
+                                          : row + h * P + p0 + (j - 2 * nv) * kVec;
+                copy_async_16(dst_tile + tt * raw_row + j * kVec, src);
+            }
         }
-        for (int idx = tid; idx < nt * N; idx += blockDim.x) {
-            const int tt = idx / N, nn = idx - tt * N;
-            const T* row = xbc + (size_t)(t0 + tt) * ld_xbc + inner + g * N + nn;
-            sB[idx] = to_f32<T>(row[0]);
-            sC[idx] = to_f32<T>(row[groups * N]);
+        copy_async_commit();
+    };
+    if (kAsync) {
+        fetch(first, 0);
+        fetch(first + kTile, 1);
+    }
+    float dt_next = 0.f;
+    if (tid < kTile && first + tid < last) dt_next = to_f32<T>(dt_raw[(size_t)(first + tid) * ld_dt + h]);
+
+    int stage = 0;
+    for (int t0 = first; t0 < last; t0 += kTile, stage ^= 1) {
+        const int nt = min(kTile, last - t0);
+        if (kAsync) copy_async_wait_all_but_one();
+        __syncthreads();
+        if (kAsync) {
+            const T* src_tile = raw + stage * raw_tile;
+            for (int idx = tid; idx < nt * N; idx += blockDim.x) {
+                const int tt = idx / N, nn = idx - tt * N;
+                const T* row = src_tile + tt * raw_row;
+                sBC[idx] = make_float2(to_f32<T>(row[nn]), to_f32<T>(row[N + nn]));
+            }
+            for (int idx = tid; idx < nt * PS; idx += blockDim.x) {
+                const int tt = idx / PS, pp = idx - tt * PS;
+                sx[idx] = to_f32<T>(src_tile[tt * raw_row + 2 * N + pp]);
+            }
+        } else {
+            for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
+                const int tt = idx / cols, pp = idx - tt * cols;
+                sx[tt * PS + pp] = to_f32<T>(xbc[(size_t)(t0 + tt) * ld_xbc + h * P + p0 + pp]);
+            }
+            for (int idx = tid; idx < nt * N; idx += blockDim.x) {
+                const int tt = idx / N, nn = idx - tt * N;
+                const T* row = xbc + (size_t)(t0 + tt) * ld_xbc + inner + g * N + nn;
+                sBC[idx] = make_float2(to_f32<T>(row[0]), to_f32<T>(row[groups * N]));
+            }
         }
         if (tid < nt) {
-            const float dt = softplus_f(to_f32<T>(dt_raw[(size_t)(t0 + tid) * ld_dt + h]) + bias);
-            sdt[tid] = dt;
-            sa[tid] = expf(-rate * dt);
+            const float dt = softplus_f(dt_next + bias);
+            sda[tid] = make_float2(dt, expf(-rate * dt));
         }
         __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float dt = sdt[tt], a = sa[tt];
-            const float xv = owner ? sx[tt * P + p] : 0.f;
-            const float dx = dt * xv;
-            float acc = 0.f;
+        if (kAsync) fetch(t0 + 2 * kTile, stage);            // the stage just widened is free again
+        if (tid < kTile && t0 + kTile + tid < last) dt_next = to_f32<T>(dt_raw[(size_t)(t0 + kTile + tid) * ld_dt + h]);
+        for (int tq = 0; tq < nt; tq += 4) {
+            float acc[4], xs[4];
 #pragma unroll
-            for (int k = 0; k < kRowsPerThread; ++k) {
-                const int n = r + R * k;
-                if (n < N) {
-                    s[k] = fmaf(a, s[k], sB[tt * N + n] * dx);
-                    acc = fmaf(s[k], sC[tt * N + n], acc);
+            for (int u = 0; u < 4; ++u) {
+                const int tt = tq + u;
+                acc[u] = 0.f;
+                xs[u] = 0.f;
+                if (tt < nt) {
+                    const float2 da = sda[tt];
+                    xs[u] = owner ? sx[tt * PS + pl] : 0.f;
+                    const float dx = da.x * xs[u];
+                    const float2* bc = sBC + tt * N + r;
+                    if (exact) {
+#pragma unroll
+                        for (int k = 0; k < KR; ++k) {
+                            const float2 v = bc[R * k];
+                            s[k] = fmaf(da.y, s[k], v.x * dx);
+                            acc[u] = fmaf(s[k], v.y, acc[u]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < KR; ++k) {
+                            if (r + R * k < N) {
+                                const float2 v = bc[R * k];
+                                s[k] = fmaf(da.y, s[k], v.x * dx);
+                                acc[u] = fmaf(s[k], v.y, acc[u]);
+                            }
+                        }
+                    }
                 }
             }
-            for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (owner && r == 0) y[(size_t)(t0 + tt) * ld_y + h * P + p] = fmaf(d_skip, xv, acc);
+            for (int o = R >> 1; o > 0; o >>= 1) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+            }
+            if (owner && r == 0) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (tq + u < nt) y[(size_t)(t0 + tq + u) * ld_y + h * P + p] = fmaf(d_skip, xs[u], acc[u]);
+            }
         }
     }
+    if (kAsync) asm volatile("cp.async.wait_all;\n" ::: "memory");
     if (owner) {
 #pragma unroll
-        for (int k = 0; k < kRowsPerThread; ++k) {
+        for (int k = 0; k < KR; ++k) {
             const int n = r + R * k;
             if (n < N) S[(size_t)n * P + p] = s[k];
         }
+    }
+}
+
+// The same recurrence for a step in which every sequence brings one token (row b
+// is sequence b's): what costs is reading and writing the state once, so a
+// thread owns four neighbouring columns of S (16-byte accesses, a row of S is one
+// contiguous run of the block's threads) for the rows n = j, j + J, ...; the J
+// partial sums of y meet in shared memory and are added in a fixed order.
+template <typename T>
+__global__ void ssm_step_kernel(const T* __restrict__ xbc, int ld_xbc, const T* __restrict__ dt_raw, int ld_dt,
+                                const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                const float* __restrict__ skip, float* __restrict__ state,
+                                float* __restrict__ y, int ld_y, const int* __restrict__ slots,
+                                int heads, int groups, int N, int P, int J) {
+    chain_release();
+    chain_wait();
+    extern __shared__ float smem[];
+    float* sB = smem;                 // N
+    float* sC = sB + N;               // N
+    float* part = sC + N;             // J * P
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int g = h / (heads / groups);
+    const int inner = heads * P, P4 = P >> 2;
+    const int tid = threadIdx.x;
+    const T* row = xbc + (size_t)b * ld_xbc;
+    for (int n = tid; n < N; n += blockDim.x) {
+        sB[n] = to_f32<T>(row[inner + g * N + n]);
+        sC[n] = to_f32<T>(row[inner + (groups + g) * N + n]);
+    }
+    const int c = tid % P4, j = tid / P4;
+    const float dt = softplus_f(to_f32<T>(dt_raw[(size_t)b * ld_dt + h]) + dt_bias[h]);
+    const float a = expf(-expf(a_log[h]) * dt);
+    float x[4], dx[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { x[i] = to_f32<T>(row[h * P + c * 4 + i]); dx[i] = dt * x[i]; }
+    __syncthreads();
+    if (j < J) {
+        float4* S = reinterpret_cast<float4*>(state + ((size_t)slots[b] * heads + h) * N * P) + c;
+        for (int n = j; n < N; n += J) {
+            float4 s = S[(size_t)n * P4];
+            const float bn = sB[n], cn = sC[n];
+            s.x = fmaf(a, s.x, bn * dx[0]); s.y = fmaf(a, s.y, bn * dx[1]);
+            s.z = fmaf(a, s.z, bn * dx[2]); s.w = fmaf(a, s.w, bn * dx[3]);
+            acc[0] = fmaf(s.x, cn, acc[0]); acc[1] = fmaf(s.y, cn, acc[1]);
+            acc[2] = fmaf(s.z, cn, acc[2]); acc[3] = fmaf(s.w, cn, acc[3]);
+            S[(size_t)n * P4] = s;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) part[j * P + c * 4 + i] = acc[i];
+    }
+    __syncthreads();
+    if (tid < P) {
+        float sum = 0.f;
+        for (int k = 0; k < J; ++k) sum += part[k * P + tid];
+        y[(size_t)b * ld_y + h * P + tid] = fmaf(skip[h], to_f32<T>(row[h * P + tid]), sum);
     }
 }
 
@@ -184,6 +394,56 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, int ld_y, cons
         out[n * ld_out + c0 + i] = from_f32<T>(v[i] * s * weight[c0 + i]);
 }
 
+// The same for bfloat16 rows where a piece is a multiple of 256 wide: one block per
+// row, a thread owns 8 neighbouring channels (16- and 32-byte accesses), a piece is
+// a whole number of warps whose sums meet through shared memory in a fixed order.
+__global__ void __launch_bounds__(1024)
+gated_rmsnorm_bf16_vec_kernel(const float* __restrict__ y, int ld_y, const bf16* __restrict__ z, int ld_z,
+                              const float* __restrict__ weight, float eps, bf16* __restrict__ out, int ld_out,
+                              int width, int size) {
+    chain_release();
+    chain_wait();
+    __shared__ float warp_ss[32];
+    const size_t n = blockIdx.x;
+    const int c = threadIdx.x * 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float v[8];
+    float ss = 0.f;
+    if (c < width) {
+        const float4* yp = reinterpret_cast<const float4*>(y + n * ld_y + c);
+        const float4 a = yp[0], b = yp[1];
+        const uint4 zr = *reinterpret_cast<const uint4*>(z + n * ld_z + c);
+        const __nv_bfloat162* zh = reinterpret_cast<const __nv_bfloat162*>(&zr);
+        const float yy[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(zh[e]);
+            v[2 * e] = yy[2 * e] * silu_f(f.x);
+            v[2 * e + 1] = yy[2 * e + 1] * silu_f(f.y);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) warp_ss[warp] = ss;
+    __syncthreads();
+    if (c < width) {
+        const int warps_per_piece = size / 256;
+        const int w0 = (warp / warps_per_piece) * warps_per_piece;
+        float total = 0.f;
+        for (int k = 0; k < warps_per_piece; ++k) total += warp_ss[w0 + k];
+        const float s = 1.0f / sqrtf(total / (float)size + eps);
+        const float4* wp = reinterpret_cast<const float4*>(weight + c);
+        const float4 w0v = wp[0], w1v = wp[1];
+        const float w[8] = {w0v.x, w0v.y, w0v.z, w0v.w, w1v.x, w1v.y, w1v.z, w1v.w};
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(v[2 * e] * s * w[2 * e], v[2 * e + 1] * s * w[2 * e + 1]);
+        *reinterpret_cast<uint4*>(out + n * ld_out + c) = o;
+    }
+}
+
 }  // namespace
 
 GTG_API int gtg_causal_conv_silu(int dtype, const void* in, int ld_in, const float* w, const float* bias,
@@ -193,9 +453,27 @@ GTG_API int gtg_causal_conv_silu(int dtype, const void* in, int ld_in, const flo
     if (n_tokens <= 0 || C <= 0) return 0;
     if (taps < 1 || ld_in < C || ld_out < C || (taps > 1 && conv_state == nullptr)) return kErrBadArgument;
     if ((C + 127) / 128 > 65535) return kErrUnsupported;
+    if (dtype == 1 && C % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && ((uintptr_t)in % 16) == 0 &&
+        ((uintptr_t)out % 16) == 0 && ((uintptr_t)conv_state % 16) == 0 && ((uintptr_t)w % 16) == 0) {
+        const int per_block = C / 8 < 128 ? (C / 8 + 31) / 32 * 32 : 128;
+        const dim3 grid_vec(n_tokens, (C / 8 + per_block - 1) / per_block);
+        return launch_chained(causal_conv_silu_bf16_vec_kernel, grid_vec, dim3(per_block), 0, stream, (const bf16*)in, ld_in, w, bias, conv_state, (bf16*)out, ld_out, token_seq, cu_seqlens, slots, C, taps);
+    }
     const dim3 grid(n_tokens, (C + 127) / 128);
     if (dtype == 0) return launch_chained(causal_conv_silu_kernel<float>, grid, dim3(128), 0, stream, (const float*)in, ld_in, w, bias, conv_state, (float*)out, ld_out, token_seq, cu_seqlens, slots, C, taps);
     if (dtype == 1) return launch_chained(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)in, ld_in, w, bias, conv_state, (bf16*)out, ld_out, token_seq, cu_seqlens, slots, C, taps);
+    return kErrBadArgument;
+}
+
+GTG_API int gtg_causal_conv_step(int dtype, const void* in, int ld_in, const float* w, const float* bias,
+                                 float* conv_state, void* out, int ld_out, const int* slots, int n_seqs, int C,
+                                 int taps, cudaStream_t stream) {
+    if (n_seqs <= 0 || C <= 0) return 0;
+    if (taps < 1 || ld_in < C || ld_out < C || (taps > 1 && conv_state == nullptr)) return kErrBadArgument;
+    if ((C + 127) / 128 > 65535) return kErrUnsupported;
+    const dim3 grid(n_seqs, (C + 127) / 128);
+    if (dtype == 0) return launch_chained(causal_conv_step_kernel<float>, grid, dim3(128), 0, stream, (const float*)in, ld_in, w, bias, conv_state, (float*)out, ld_out, slots, C, taps);
+    if (dtype == 1) return launch_chained(causal_conv_step_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)in, ld_in, w, bias, conv_state, (bf16*)out, ld_out, slots, C, taps);
     return kErrBadArgument;
 }
 
@@ -210,37 +488,84 @@ GTG_API int gtg_conv_state_update(int dtype, const void* in, int ld_in, float* c
 }
 
 // How many threads share a column of the state: the least power of two that
-// leaves a thread at most kRowsPerThread rows, widened while the block stays small.
-static int scan_split(int N, int P) {
+// leaves a thread at most kRowsPerThread rows (few threads per column mean few
+// shuffle rounds per token), but a warp's worth of threads in the block at least.
+static int scan_split(int N, int cols) {
     int R = 1;
     while (R < 32 && (N + R - 1) / R > kRowsPerThread) R *= 2;
-    while (R < 32 && R * 2 <= N && P * R * 2 <= 256) R *= 2;
+    while (R < 32 && R * 2 <= N && cols * R < 32) R *= 2;
     return R;
 }
 
 GTG_API int gtg_ssm_scan(int dtype, const void* xbc, int ld_xbc, const void* dt_raw, int ld_dt,
                          const float* dt_bias, const float* a_log, const float* skip, float* state,
                          float* y, int ld_y, const int* cu_seqlens, const int* slots, int n_seqs,
-                         int heads, int groups, int N, int P, cudaStream_t stream) {
+                         int heads, int groups, int N, int P, int one_token_each, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0) return kErrBadArgument;
     if (n_seqs > 65535) return kErrUnsupported;
-    const int R = scan_split(N, P);
+    if (one_token_each && P % 4 == 0 && P <= 1024 && ((uintptr_t)state % 16) == 0) {
+        const int P4 = P / 4;
+        int J = 256 / P4;
+        if (J < 1) J = 1;
+        if (J > N) J = N;
+        int threads = (P4 * J + 31) / 32 * 32;
+        if (threads < P) threads = (P + 31) / 32 * 32;
+        const size_t smem_step = (size_t)(2 * N + J * P) * sizeof(float);
+        if (threads <= 1024 && smem_step <= 48 * 1024) {
+            const dim3 grid_step(heads, n_seqs);
+            if (dtype == 0) return launch_chained(ssm_step_kernel<float>, grid_step, dim3(threads), smem_step, stream, (const float*)xbc, ld_xbc, (const float*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, slots, heads, groups, N, P, J);
+            if (dtype == 1) return launch_chained(ssm_step_kernel<bf16>, grid_step, dim3(threads), smem_step, stream, (const bf16*)xbc, ld_xbc, (const bf16*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, slots, heads, groups, N, P, J);
+            return kErrBadArgument;
+        }
+    }
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
+            n_sm = 148;
+    }
+    // Slices of columns, so that a few long sequences still give about three blocks per
+    // multiprocessor.  Where every run of x, B and C starts on a 16-byte boundary the
+    // slices are halves, quarters, ... of a head that keep that alignment and the rows
+    // come by asynchronous copies; otherwise slices of at least four columns, read plainly.
+    const int vec = dtype == 0 ? 4 : 8;
+    const bool aligned = N % vec == 0 && P % vec == 0 && ld_xbc % vec == 0 && ((uintptr_t)xbc % 16) == 0;
+    int PS = P;
+    if (aligned) {
+        while ((long long)heads * n_seqs * (P / PS) < 3LL * n_sm && PS % 2 == 0 && (PS / 2) % vec == 0) PS /= 2;
+    } else {
+        int slices = (3 * n_sm + heads * n_seqs - 1) / (heads * n_seqs);
+        if (slices > (P + 3) / 4) slices = (P + 3) / 4;
+        if (slices < 1) slices = 1;
+        PS = (P + slices - 1) / slices;
+    }
+    const int slices = (P + PS - 1) / PS;
+    const int R = scan_split(N, PS);
     if ((N + R - 1) / R > kRowsPerThread) return kErrUnsupported;
-    const int threads = (P * R + 31) / 32 * 32;
+    const int threads = (PS * R + 31) / 32 * 32;
     if (threads > 1024) return kErrUnsupported;
-    const size_t smem = (size_t)(kTile * (P + 2 * N) + 2 * kTile) * sizeof(float);
+    size_t smem = (size_t)(kTile * (PS + 2 * N) + 2 * kTile) * sizeof(float);
+    if (aligned) smem += (size_t)2 * kTile * (2 * N + PS) * (dtype == 0 ? 4 : 2);
     if (smem > 200 * 1024) return kErrUnsupported;
-    const dim3 grid(heads, n_seqs);
+    const dim3 grid(heads, n_seqs, slices);
     cudaError_t e;
-    if (dtype == 0) {
-        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(ssm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-        return launch_chained(ssm_scan_kernel<float>, grid, dim3(threads), smem, stream, (const float*)xbc, ld_xbc, (const float*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, cu_seqlens, slots, heads, groups, N, P, R);
-    }
-    if (dtype == 1) {
-        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(ssm_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-        return launch_chained(ssm_scan_kernel<bf16>, grid, dim3(threads), smem, stream, (const bf16*)xbc, ld_xbc, (const bf16*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, cu_seqlens, slots, heads, groups, N, P, R);
-    }
+    const int rows = (N + R - 1) / R;
+#define GTG_SCAN_LAUNCH_KR(T, ASYNC, KR)                                                                                 \
+    do {                                                                                                                 \
+        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(ssm_scan_kernel<T, ASYNC, KR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e; \
+        return launch_chained(ssm_scan_kernel<T, ASYNC, KR>, grid, dim3(threads), smem, stream, (const T*)xbc, ld_xbc, (const T*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, cu_seqlens, slots, heads, groups, N, P, R, PS); \
+    } while (0)
+#define GTG_SCAN_LAUNCH(T, ASYNC)                                                                                        \
+    do {                                                                                                                 \
+        if (rows <= 4) GTG_SCAN_LAUNCH_KR(T, ASYNC, 4);                                                                  \
+        if (rows <= 8) GTG_SCAN_LAUNCH_KR(T, ASYNC, 8);                                                                  \
+        GTG_SCAN_LAUNCH_KR(T, ASYNC, 16);                                                                                \
+    } while (0)
+    if (dtype == 0) { if (aligned) GTG_SCAN_LAUNCH(float, true); else GTG_SCAN_LAUNCH(float, false); }
+    if (dtype == 1) { if (aligned) GTG_SCAN_LAUNCH(bf16, true); else GTG_SCAN_LAUNCH(bf16, false); }
+#undef GTG_SCAN_LAUNCH_KR
+#undef GTG_SCAN_LAUNCH
     return kErrBadArgument;
 }
 
@@ -250,6 +575,9 @@ GTG_API int gtg_gated_rmsnorm(int dtype, const float* y, int ld_y, const void* z
     if (n_rows <= 0 || width <= 0) return 0;
     if (parts <= 0 || width % parts || parts > 65535) return kErrBadArgument;
     const int size = width / parts;
+    if (dtype == 1 && size % 256 == 0 && width <= 8192 && ld_y % 4 == 0 && ld_z % 8 == 0 && ld_out % 8 == 0 &&
+        ((uintptr_t)y % 16) == 0 && ((uintptr_t)z % 16) == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)weight % 16) == 0)
+        return launch_chained(gated_rmsnorm_bf16_vec_kernel, dim3(n_rows), dim3(width / 8), 0, stream, y, ld_y, (const bf16*)z, ld_z, weight, eps, (bf16*)out, ld_out, width, size);
     int threads = 32;
     while (threads < 512 && threads * 2 < size) threads *= 2;
     const size_t smem = (size_t)(size + 33) * sizeof(float);

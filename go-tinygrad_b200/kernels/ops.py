@@ -32,7 +32,8 @@ _SIGNATURES = {
     "gtg_hidden_concat": ("elementwise", [_I, _P, _P, _P, _P, _I, _I, _P]),
     "gtg_causal_conv_silu": ("ssm", [_I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _P]),
     "gtg_conv_state_update": ("ssm", [_I, _P, _I, _P, _P, _P, _I, _I, _I, _P]),
-    "gtg_ssm_scan": ("ssm", [_I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_ssm_scan": ("ssm", [_I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "gtg_causal_conv_step": ("ssm", [_I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _P]),
     "gtg_gated_rmsnorm": ("ssm", [_I, _P, _I, _P, _I, _P, _F, _P, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_simt": ("gemm_f32", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_advance": ("elementwise", [_P, _P, _P, _P, _I, _P]),
@@ -395,24 +396,36 @@ def _int32(name: str, *tensors) -> None:
 
 
 def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
-                     conv_state: torch.Tensor, out: torch.Tensor, token_seq, cu_seqlens, slots) -> None:
-    """out[n, c] = silu(bias[c] + sum_j weight[c, j] x[n - (taps-1-j), c]) within each
+                     conv_state: torch.Tensor, out: torch.Tensor, token_seq, cu_seqlens, slots,
+                     n_seqs: Optional[int] = None, update_state: bool = False, one_token_each: bool = False) -> None:
+    """out[n, c] = silu(bias[c] + sum_j weight[j, c] x[n - (taps-1-j), c]) (weight is
+    held tap by tap, [taps, C]; the last tap is the current token's) within each
     sequence of the packed rows; what precedes a sequence's first row of the step
-    comes from conv_state[slot] ([taps-1, C] float32, oldest first)."""
+    comes from conv_state[slot] ([taps-1, C] float32, oldest first).  With
+    `update_state` the state is then left as `conv_state_update` leaves it (one
+    kernel does both when every sequence brings one token: `one_token_each`)."""
     _rows2d(x, "causal_conv_silu: x"); _rows2d(out, "causal_conv_silu: out")
     n, C = x.shape
-    taps = weight.shape[1]
+    taps = weight.shape[0]
     _need(out.dtype == x.dtype and tuple(out.shape) == (n, C), "causal_conv_silu: out must match x")
-    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == C,
-          "causal_conv_silu: weight must be float32 [C, taps]")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.dim() == 2 and weight.shape[1] == C,
+          "causal_conv_silu: weight must be float32 [taps, C]")
     _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C),
           "causal_conv_silu: bias must be float32 [C]")
     _need(conv_state.dtype == torch.float32 and conv_state.is_contiguous()
           and tuple(conv_state.shape[1:]) == (taps - 1, C), "causal_conv_silu: conv_state must be float32 [slots, taps-1, C]")
     _int32("causal_conv_silu", token_seq, cu_seqlens, slots)
+    if update_state and one_token_each:
+        _need(n == slots.numel(), "causal_conv_silu: one token each means as many rows as sequences")
+        _check(_fn("gtg_causal_conv_step")(_dt(x), _ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(conv_state),
+                                           _ptr(out), out.stride(0), _ptr(slots), n, C, taps, _stream()),
+               "causal_conv_silu(step)")
+        return
     _check(_fn("gtg_causal_conv_silu")(_dt(x), _ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(conv_state),
                                        _ptr(out), out.stride(0), _ptr(token_seq), _ptr(cu_seqlens), _ptr(slots),
                                        n, C, taps, _stream()), "causal_conv_silu")
+    if update_state:
+        conv_state_update(x, conv_state, cu_seqlens, slots, slots.numel() if n_seqs is None else n_seqs)
 
 
 def conv_state_update(x: torch.Tensor, conv_state: torch.Tensor, cu_seqlens, slots, n_seqs: int) -> None:
@@ -429,12 +442,13 @@ def conv_state_update(x: torch.Tensor, conv_state: torch.Tensor, cu_seqlens, slo
 
 def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
              skip: torch.Tensor, state: torch.Tensor, y: torch.Tensor, cu_seqlens, slots, n_seqs: int,
-             heads: int, groups: int, n_state: int, head_dim: int) -> None:
+             heads: int, groups: int, n_state: int, head_dim: int, one_token_each: bool = False) -> None:
     """The state-space recurrence with a scalar decay per head, token by token:
     xbc [n, heads*P + 2*groups*N] = [x | B | C] per row, dt_raw [n, heads];
     dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T,
     y = S^T C + skip * x.  state: float32 [slots, heads, N, P], read and left
-    per sequence; y: float32 [n, heads*P]."""
+    per sequence; y: float32 [n, heads*P].  `one_token_each`: row b is sequence
+    b's only token (a decode step), which a kernel of its own serves."""
     _rows2d(xbc, "ssm_scan: xbc"); _rows2d(dt_raw, "ssm_scan: dt_raw"); _rows2d(y, "ssm_scan: y")
     n = xbc.shape[0]
     inner = heads * head_dim
@@ -448,7 +462,8 @@ def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_l
     _int32("ssm_scan", cu_seqlens, slots)
     _check(_fn("gtg_ssm_scan")(_dt(xbc), _ptr(xbc), xbc.stride(0), _ptr(dt_raw), dt_raw.stride(0), _ptr(dt_bias),
                                _ptr(a_log), _ptr(skip), _ptr(state), _ptr(y), y.stride(0), _ptr(cu_seqlens), _ptr(slots),
-                               int(n_seqs), heads, groups, n_state, head_dim, _stream()), "ssm_scan")
+                               int(n_seqs), heads, groups, n_state, head_dim, 1 if one_token_each and n == n_seqs else 0,
+                               _stream()), "ssm_scan")
 
 
 def gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,

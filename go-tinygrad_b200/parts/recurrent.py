@@ -80,7 +80,7 @@ class Mamba2(Mixer):
         n = self.names
         self.w_in = rt.matrix(tensors[n["in"]])
         self.w_o = rt.matrix(tensors[n["o"]])
-        self.conv_w = rt.vector(tensors[n["conv"]])
+        self.conv_w = rt.vector(tensors[n["conv"]].t().contiguous())      # tap by tap: [taps, channels]
         self.conv_b = rt.vector(tensors[n["conv_bias"]])
         self.dt_bias = rt.vector(tensors[n["dt_bias"]])
         self.a_log = rt.vector(tensors[n["a_log"]])
@@ -101,12 +101,13 @@ class Mamba2(Mixer):
         conv_state, ssm_state = cache.state("conv"), cache.state("ssm")
         xbc = rt.empty(n, self.conv_dim)
         ops.causal_conv_silu(conv_in, self.conv_w, self.conv_b, conv_state, xbc,
-                             ctx.token_seq, ctx.cu_seqlens, ctx.slots)
-        ops.conv_state_update(conv_in, conv_state, ctx.cu_seqlens, ctx.slots, ctx.n_seqs)
+                             ctx.token_seq, ctx.cu_seqlens, ctx.slots, n_seqs=ctx.n_seqs, update_state=True,
+                             one_token_each=ctx.is_decode)
         ctx.trace("conv", xbc)
         y = rt.empty(n, self.inner, dtype=torch.float32)
         ops.ssm_scan(xbc, dt_raw, self.dt_bias, self.a_log, self.d, ssm_state, y, ctx.cu_seqlens, ctx.slots,
-                     ctx.n_seqs, self.n_heads, self.n_groups, self.n_state, self.head_dim)
+                     ctx.n_seqs, self.n_heads, self.n_groups, self.n_state, self.head_dim,
+                     one_token_each=ctx.is_decode)
         ctx.trace("scan", y)
         gated = rt.empty(n, self.inner)
         ops.gated_rmsnorm(y, z, self.norm_w, self.eps, gated, self.norm_parts)

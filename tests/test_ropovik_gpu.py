@@ -187,8 +187,11 @@ def test_convolution_carries_its_last_inputs_across_portions(dtype):
             rows = list(range(at, at + n)) + list(range(T + at, T + at + n))
             xin, out = x[rows].contiguous(), torch.empty(2 * n, C, dtype=TORCH[dtype], device=DEV)
             seq, cu, slots = i32([0] * n + [1] * n), i32([0, n, 2 * n]), i32([3, 0])
-            ops.causal_conv_silu(xin, t32(w), t32(b), state, out, seq, cu, slots)
-            ops.conv_state_update(xin, state, cu, slots, 2)
+            if n == 1:                                      # one token each: convolution and state in one kernel
+                ops.causal_conv_silu(xin, t32(w.T.copy()), t32(b), state, out, seq, cu, slots, update_state=True, one_token_each=True)
+            else:
+                ops.causal_conv_silu(xin, t32(w.T.copy()), t32(b), state, out, seq, cu, slots)
+                ops.conv_state_update(xin, state, cu, slots, 2)
             got[rows] = out
             at += n
         lim = 1e-5 if dtype == "float32" else 1e-2
@@ -221,7 +224,7 @@ def test_recurrence_keeps_its_state_across_portions_and_remembers_far_tokens(dty
                                   xs[1:, inner:inner + groups * N].reshape(T - 1, groups, N),
                                   xs[1:, inner + groups * N:].reshape(T - 1, groups, N), skip).reshape(T - 1, inner)
     assert np.abs(want[-1, :P] - forgot[-1, :P]).max() > 0.05 * np.abs(want[-1, :P]).max()   # the test can see token 0
-    for portions in ([T], [1], [15, 16, 17, 1, 2, 33]):
+    for portions in ([T], [1], [15, 16, 17, 1, 2, 33], [100, 1]):
         state = torch.zeros(3, heads, N, P, device=DEV)
         got = torch.zeros(T, inner, device=DEV)
         at, i = 0, 0
@@ -229,7 +232,7 @@ def test_recurrence_keeps_its_state_across_portions_and_remembers_far_tokens(dty
             n = min(portions[min(i, len(portions) - 1)], T - at)
             y = torch.empty(n, inner, device=DEV)
             ops.ssm_scan(xbc[at:at + n], dt_raw[at:at + n], t32(dt_bias), t32(a_log), t32(skip), state, y,
-                         i32([0, n]), i32([2]), 1, heads, groups, N, P)
+                         i32([0, n]), i32([2]), 1, heads, groups, N, P, one_token_each=(n == 1 and portions != [1]))
             got[at:at + n] = y
             at += n
             i += 1
@@ -240,7 +243,7 @@ def test_recurrence_keeps_its_state_across_portions_and_remembers_far_tokens(dty
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_gate_then_norm_in_pieces(dtype):
     rng = np.random.default_rng(3)
-    for width, parts in ((48, 1), (48, 3), (640, 2), (96, 96)):
+    for width, parts in ((48, 1), (48, 3), (640, 2), (96, 96), (1024, 2), (768, 3), (2048, 1)):
         y, z, w = rng.standard_normal((7, width)) * 4, rng.standard_normal((7, width)), rng.standard_normal(width)
         zt = t32(z).to(TORCH[dtype])
         out = torch.empty(7, width, dtype=TORCH[dtype], device=DEV)
