@@ -593,17 +593,17 @@ def run_design(args):
             conv_in, z, dt_raw = proj[:, inner:inner + conv_dim], proj[:, :inner], proj[:, inner + conv_dim:]
             cw, cb = rnd(taps, conv_dim, dtype=f32), rnd(conv_dim, dtype=f32)
             cstate = torch.zeros(n_seqs, taps - 1, conv_dim, device=dev)
-            xbc = torch.empty(n, conv_dim, dtype=bf, device=dev)
+            xs, bc = torch.empty(n, inner, dtype=bf, device=dev), torch.empty(n, G * N, 2, device=dev)
             add(f"causal_conv_silu + state ({tag})", n,
-                timed(lambda: ops.causal_conv_silu(conv_in, cw, cb, cstate, xbc, seq, cu, slots, n_seqs=n_seqs,
-                                                   update_state=True, one_token_each=one)),
-                n * conv_dim * 4 + (2 * n_seqs * (taps - 1) * conv_dim * 4 if one else 0))
+                timed(lambda: ops.causal_conv_silu(conv_in, cw, cb, cstate, xs, seq, cu, slots, n_seqs=n_seqs,
+                                                   update_state=True, one_token_each=one, pairs=bc)),
+                n * (conv_dim * 2 + inner * 2 + 2 * G * N * 4) + (2 * n_seqs * (taps - 1) * conv_dim * 4 if one else 0))
             dtb, al, sk = rnd(heads, dtype=f32) - 2.0, rnd(heads, dtype=f32), rnd(heads, dtype=f32)
             sstate = torch.zeros(n_seqs, heads, N, P, device=dev)
             y = torch.empty(n, inner, dtype=f32, device=dev)
-            scan_bytes = n * (conv_dim * 2 + inner * 4) + 2 * n_seqs * heads * N * P * 4
+            scan_bytes = n * (inner * 2 + 2 * G * N * 4 + inner * 4) + 2 * n_seqs * heads * N * P * 4
             add(f"ssm_scan ({tag})", n,
-                timed(lambda: ops.ssm_scan(xbc, dt_raw, dtb, al, sk, sstate, y, cu, slots, n_seqs, heads, G, N, P,
+                timed(lambda: ops.ssm_scan(xs, bc, dt_raw, dtb, al, sk, sstate, y, cu, slots, n_seqs, heads, G, N, P,
                                            one_token_each=one)), scan_bytes)
             gated, norm_w = torch.empty(n, inner, dtype=bf, device=dev), torch.ones(inner, device=dev)
             add(f"gated_rmsnorm ({tag})", n, timed(lambda: ops.gated_rmsnorm(y, z, norm_w, 1e-5, gated, G)),

@@ -13,6 +13,12 @@
 namespace {
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+// Where channel c >= n_plain of row n lands among the pairs: run U first, then V.
+__device__ __forceinline__ size_t pair_index(size_t n, int c, int n_plain, int C) {
+    const int half = (C - n_plain) >> 1, q = c - n_plain;
+    return n * 2 * half + (q < half ? 2 * q : 2 * (q - half) + 1);
+}
 // log(1 + exp(x)) without overflow and without a cut-off
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
@@ -22,13 +28,16 @@ __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + lo
 // channels read neighbouring weights.  Inputs before the first row of the step come from
 // conv_state[slot, taps-1, C] (the sequence's last taps-1 inputs, oldest first;
 // zero for a new sequence).  The sum runs in the same order however the
-// sequence was cut into steps.
+// sequence was cut into steps.  The first n_plain channels go to `out`; the rest,
+// two equal runs U and V (the B and C of a recurrence), go to `pairs` as float
+// (U_q, V_q) side by side, [row][q][2], the form in which the recurrence reads
+// them; pairs == nullptr: every channel goes to `out`.
 template <typename T>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int ld_in, const float* __restrict__ w,
                                         const float* __restrict__ bias, const float* __restrict__ conv_state,
                                         T* __restrict__ out, int ld_out, const int* __restrict__ token_seq,
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
-                                        int C, int taps) {
+                                        int C, int taps, int n_plain, float* __restrict__ pairs) {
     chain_release();
     chain_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -45,7 +54,8 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int ld_in, con
                                       : st[(size_t)(keep + i - back) * C + c];
         acc = fmaf(w[(size_t)j * C + c], v, acc);
     }
-    out[(size_t)n * ld_out + c] = from_f32<T>(silu_f(acc));
+    if (c < n_plain) out[(size_t)n * ld_out + c] = from_f32<T>(silu_f(acc));
+    else pairs[pair_index(n, c, n_plain, C)] = silu_f(acc);
 }
 
 // The same for bfloat16 rows of 16-byte aligned runs: a thread takes 8 neighbouring
@@ -54,7 +64,7 @@ __global__ void causal_conv_silu_bf16_vec_kernel(const bf16* __restrict__ in, in
                                                  const float* __restrict__ bias, const float* __restrict__ conv_state,
                                                  bf16* __restrict__ out, int ld_out, const int* __restrict__ token_seq,
                                                  const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
-                                                 int C, int taps) {
+                                                 int C, int taps, int n_plain, float* __restrict__ pairs) {
     chain_release();
     chain_wait();
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
@@ -85,6 +95,11 @@ __global__ void causal_conv_silu_bf16_vec_kernel(const bf16* __restrict__ in, in
         const float wj[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = fmaf(wj[e], v[e], acc[e]);
+    }
+    if (c >= n_plain) {                      // n_plain and the runs are multiples of 8: a thread's channels stay together
+#pragma unroll
+        for (int e = 0; e < 8; ++e) pairs[pair_index(n, c + e, n_plain, C)] = silu_f(acc[e]);
+        return;
     }
     uint4 o;
     __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
@@ -121,7 +136,7 @@ template <typename T>
 __global__ void causal_conv_step_kernel(const T* __restrict__ in, int ld_in, const float* __restrict__ w,
                                         const float* __restrict__ bias, float* __restrict__ conv_state,
                                         T* __restrict__ out, int ld_out, const int* __restrict__ slots,
-                                        int C, int taps) {
+                                        int C, int taps, int n_plain, float* __restrict__ pairs) {
     chain_release();
     chain_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -138,7 +153,8 @@ __global__ void causal_conv_step_kernel(const T* __restrict__ in, int ld_in, con
     }
     acc = fmaf(w[(size_t)keep * C + c], cur, acc);
     if (keep > 0) st[(size_t)(keep - 1) * C + c] = cur;
-    out[(size_t)b * ld_out + c] = from_f32<T>(silu_f(acc));
+    if (c < n_plain) out[(size_t)b * ld_out + c] = from_f32<T>(silu_f(acc));
+    else pairs[pair_index(b, c, n_plain, C)] = silu_f(acc);
 }
 
 // ------------------------------------------- the recurrence, token by token
@@ -163,30 +179,33 @@ __device__ __forceinline__ void copy_async_16(void* smem_dst, const void* gmem_s
 __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 __device__ __forceinline__ void copy_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
 
-// kAsync: the rows of x, B and C are 16-byte aligned runs, fetched two tiles ahead
-// by asynchronous copies into a raw staging area and widened to float from there;
-// otherwise (odd sizes) they are read element by element when their tile begins.
+// x: [row][heads * P] of T; bc: [row][groups * N] float pairs (B_n, C_n), as the
+// convolution leaves them.  kAsync: the runs a block needs are 16-byte aligned and
+// arrive one tile ahead by asynchronous copies, the pairs straight into the place
+// the arithmetic reads them from; otherwise (odd sizes) they are read plainly when
+// their tile begins.
 // KR: rows of S a thread owns (R * KR >= N; the rows beyond N, if any, are skipped).
-template <typename T, bool kAsync, int KR>
-__global__ void ssm_scan_kernel(const T* __restrict__ xbc, int ld_xbc, const T* __restrict__ dt_raw, int ld_dt,
+// RT: R known when compiling, with N = RT * KR (every offset into the staged pairs
+// is then a constant), or 0: R and N as passed.
+template <typename T, bool kAsync, int KR, int RT>
+__global__ void ssm_scan_kernel(const T* __restrict__ x, int ld_x, const float2* __restrict__ bc, int ld_bc,
+                                const T* __restrict__ dt_raw, int ld_dt,
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                 const float* __restrict__ skip, float* __restrict__ state,
                                 float* __restrict__ y, int ld_y, const int* __restrict__ cu_seqlens,
-                                const int* __restrict__ slots, int heads, int groups, int N, int P, int R, int PS) {
+                                const int* __restrict__ slots, int heads, int groups, int N_, int P, int R_, int PS) {
     chain_release();
     chain_wait();
     extern __shared__ __align__(16) float smem[];
     constexpr int kVec = 16 / (int)sizeof(T);
-    float2* sBC = reinterpret_cast<float2*>(smem);          // kTile * N pairs (B, C)
-    float* sx = smem + 2 * kTile * N;                       // kTile * PS
-    float2* sda = reinterpret_cast<float2*>(sx + kTile * PS);   // kTile pairs (dt, a)
-    // raw staging, two tiles: per token [B: N | C: N | x: PS] of T (kAsync only)
-    T* raw = reinterpret_cast<T*>(sda + kTile);
-    const int raw_row = 2 * N + PS, raw_tile = kTile * raw_row;
+    const int R = RT ? RT : R_, N = RT ? RT * KR : N_;
+    float2* sBC = reinterpret_cast<float2*>(smem);          // two tiles of kTile * N pairs
+    float* sx = smem + 4 * kTile * N;                       // kTile * PS
+    float2* sda = reinterpret_cast<float2*>(sx + kTile * PS + ((kTile * PS) & 1));   // kTile pairs (dt, a)
+    T* rawx = reinterpret_cast<T*>(sda + kTile);            // two tiles of kTile * PS (kAsync only)
     const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * PS;
     const int cols = min(PS, P - p0);
     const int g = h / (heads / groups);
-    const int inner = heads * P;
     const int tid = threadIdx.x;
     const int pl = tid / R, r = tid - pl * R;
     const bool owner = pl < cols;
@@ -200,57 +219,43 @@ __global__ void ssm_scan_kernel(const T* __restrict__ xbc, int ld_xbc, const T* 
         s[k] = (owner && n < N) ? S[(size_t)n * P + p] : 0.f;
     }
     const float bias = dt_bias[h], rate = expf(a_log[h]), d_skip = skip[h];
-    const bool exact = R * KR == N;                          // no row of a thread lies beyond N
+    const bool exact = RT != 0 || R * KR == N;               // no row of a thread lies beyond N
 
-    // one tile's rows into raw stage `stage`; always one commit, so that groups count tiles
+    // one tile's rows into stage `stage`; always one commit, so that groups count tiles
     auto fetch = [&](int t0, int stage) {
         if (t0 < last) {
             const int nt = min(kTile, last - t0);
-            const int nv = N / kVec, xv = PS / kVec, per_row = 2 * nv + xv;
-            T* dst_tile = raw + stage * raw_tile;
+            const int nv = N / 2, xv = PS / kVec, per_row = nv + xv;
             for (int v = tid; v < nt * per_row; v += blockDim.x) {
                 const int tt = v / per_row, j = v - tt * per_row;
-                const T* row = xbc + (size_t)(t0 + tt) * ld_xbc;
-                const T* src = j < nv ? row + inner + g * N + j * kVec
-                             : j < 2 * nv ? row + inner + (groups + g) * N + (j - nv) * kVec
-                                          : row + h * P + p0 + (j - 2 * nv) * kVec;
-                copy_async_16(dst_tile + tt * raw_row + j * kVec, src);
+                if (j < nv) copy_async_16(sBC + (stage * kTile + tt) * N + 2 * j, bc + (size_t)(t0 + tt) * ld_bc + g * N + 2 * j);
+                else copy_async_16(rawx + (stage * kTile + tt) * PS + (j - nv) * kVec,
+                                   x + (size_t)(t0 + tt) * ld_x + h * P + p0 + (j - nv) * kVec);
             }
         }
         copy_async_commit();
     };
-    if (kAsync) {
-        fetch(first, 0);
-        fetch(first + kTile, 1);
-    }
+    if (kAsync) fetch(first, 0);
     float dt_next = 0.f;
     if (tid < kTile && first + tid < last) dt_next = to_f32<T>(dt_raw[(size_t)(first + tid) * ld_dt + h]);
 
     int stage = 0;
     for (int t0 = first; t0 < last; t0 += kTile, stage ^= 1) {
         const int nt = min(kTile, last - t0);
-        if (kAsync) copy_async_wait_all_but_one();
-        __syncthreads();
+        __syncthreads();                                     // the tile before has been used up: its stage is free
         if (kAsync) {
-            const T* src_tile = raw + stage * raw_tile;
-            for (int idx = tid; idx < nt * N; idx += blockDim.x) {
-                const int tt = idx / N, nn = idx - tt * N;
-                const T* row = src_tile + tt * raw_row;
-                sBC[idx] = make_float2(to_f32<T>(row[nn]), to_f32<T>(row[N + nn]));
-            }
-            for (int idx = tid; idx < nt * PS; idx += blockDim.x) {
-                const int tt = idx / PS, pp = idx - tt * PS;
-                sx[idx] = to_f32<T>(src_tile[tt * raw_row + 2 * N + pp]);
-            }
+            fetch(t0 + kTile, stage ^ 1);
+            copy_async_wait_all_but_one();
+            __syncthreads();
+            for (int idx = tid; idx < nt * PS; idx += blockDim.x) sx[idx] = to_f32<T>(rawx[stage * kTile * PS + idx]);
         } else {
             for (int idx = tid; idx < nt * cols; idx += blockDim.x) {
                 const int tt = idx / cols, pp = idx - tt * cols;
-                sx[tt * PS + pp] = to_f32<T>(xbc[(size_t)(t0 + tt) * ld_xbc + h * P + p0 + pp]);
+                sx[tt * PS + pp] = to_f32<T>(x[(size_t)(t0 + tt) * ld_x + h * P + p0 + pp]);
             }
             for (int idx = tid; idx < nt * N; idx += blockDim.x) {
                 const int tt = idx / N, nn = idx - tt * N;
-                const T* row = xbc + (size_t)(t0 + tt) * ld_xbc + inner + g * N + nn;
-                sBC[idx] = make_float2(to_f32<T>(row[0]), to_f32<T>(row[groups * N]));
+                sBC[(stage * kTile + tt) * N + nn] = bc[(size_t)(t0 + tt) * ld_bc + g * N + nn];
             }
         }
         if (tid < nt) {
@@ -258,32 +263,47 @@ __global__ void ssm_scan_kernel(const T* __restrict__ xbc, int ld_xbc, const T* 
             sda[tid] = make_float2(dt, expf(-rate * dt));
         }
         __syncthreads();
-        if (kAsync) fetch(t0 + 2 * kTile, stage);            // the stage just widened is free again
         if (tid < kTile && t0 + kTile + tid < last) dt_next = to_f32<T>(dt_raw[(size_t)(t0 + kTile + tid) * ld_dt + h]);
+        const float2* tile_bc = sBC + stage * kTile * N + r;
         for (int tq = 0; tq < nt; tq += 4) {
             float acc[4], xs[4];
+            if (exact && tq + 4 <= nt) {
+                // four whole tokens, no branch in the way: the rows' chains (one per k) run side
+                // by side, each stepping through the four tokens in order
+                float da_a[4], dx[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int tt = tq + u;
-                acc[u] = 0.f;
-                xs[u] = 0.f;
-                if (tt < nt) {
-                    const float2 da = sda[tt];
-                    xs[u] = owner ? sx[tt * PS + pl] : 0.f;
-                    const float dx = da.x * xs[u];
-                    const float2* bc = sBC + tt * N + r;
-                    if (exact) {
+                for (int u = 0; u < 4; ++u) {
+                    const float2 da = sda[tq + u];
+                    xs[u] = owner ? sx[(tq + u) * PS + pl] : 0.f;
+                    da_a[u] = da.y;
+                    dx[u] = da.x * xs[u];
+                    acc[u] = 0.f;
+                }
+                const float2* row = tile_bc + tq * N;
 #pragma unroll
-                        for (int k = 0; k < KR; ++k) {
-                            const float2 v = bc[R * k];
-                            s[k] = fmaf(da.y, s[k], v.x * dx);
-                            acc[u] = fmaf(s[k], v.y, acc[u]);
-                        }
-                    } else {
+                for (int k = 0; k < KR; ++k) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float2 v = row[u * N + R * k];
+                        s[k] = fmaf(da_a[u], s[k], v.x * dx[u]);
+                        acc[u] = fmaf(s[k], v.y, acc[u]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int tt = tq + u;
+                    acc[u] = 0.f;
+                    xs[u] = 0.f;
+                    if (tt < nt) {
+                        const float2 da = sda[tt];
+                        xs[u] = owner ? sx[tt * PS + pl] : 0.f;
+                        const float dx = da.x * xs[u];
+                        const float2* row = tile_bc + tt * N;
 #pragma unroll
                         for (int k = 0; k < KR; ++k) {
                             if (r + R * k < N) {
-                                const float2 v = bc[R * k];
+                                const float2 v = row[R * k];
                                 s[k] = fmaf(da.y, s[k], v.x * dx);
                                 acc[u] = fmaf(s[k], v.y, acc[u]);
                             }
@@ -318,7 +338,8 @@ __global__ void ssm_scan_kernel(const T* __restrict__ xbc, int ld_xbc, const T* 
 // contiguous run of the block's threads) for the rows n = j, j + J, ...; the J
 // partial sums of y meet in shared memory and are added in a fixed order.
 template <typename T>
-__global__ void ssm_step_kernel(const T* __restrict__ xbc, int ld_xbc, const T* __restrict__ dt_raw, int ld_dt,
+__global__ void ssm_step_kernel(const T* __restrict__ x, int ld_x, const float2* __restrict__ bc, int ld_bc,
+                                const T* __restrict__ dt_raw, int ld_dt,
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                 const float* __restrict__ skip, float* __restrict__ state,
                                 float* __restrict__ y, int ld_y, const int* __restrict__ slots,
@@ -331,19 +352,20 @@ __global__ void ssm_step_kernel(const T* __restrict__ xbc, int ld_xbc, const T* 
     float* part = sC + N;             // J * P
     const int h = blockIdx.x, b = blockIdx.y;
     const int g = h / (heads / groups);
-    const int inner = heads * P, P4 = P >> 2;
+    const int P4 = P >> 2;
     const int tid = threadIdx.x;
-    const T* row = xbc + (size_t)b * ld_xbc;
+    const T* row = x + (size_t)b * ld_x;
     for (int n = tid; n < N; n += blockDim.x) {
-        sB[n] = to_f32<T>(row[inner + g * N + n]);
-        sC[n] = to_f32<T>(row[inner + (groups + g) * N + n]);
+        const float2 v = bc[(size_t)b * ld_bc + g * N + n];
+        sB[n] = v.x;
+        sC[n] = v.y;
     }
     const int c = tid % P4, j = tid / P4;
     const float dt = softplus_f(to_f32<T>(dt_raw[(size_t)b * ld_dt + h]) + dt_bias[h]);
     const float a = expf(-expf(a_log[h]) * dt);
-    float x[4], dx[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float xv[4], dx[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { x[i] = to_f32<T>(row[h * P + c * 4 + i]); dx[i] = dt * x[i]; }
+    for (int i = 0; i < 4; ++i) { xv[i] = to_f32<T>(row[h * P + c * 4 + i]); dx[i] = dt * xv[i]; }
     __syncthreads();
     if (j < J) {
         float4* S = reinterpret_cast<float4*>(state + ((size_t)slots[b] * heads + h) * N * P) + c;
@@ -449,31 +471,36 @@ gated_rmsnorm_bf16_vec_kernel(const float* __restrict__ y, int ld_y, const bf16*
 GTG_API int gtg_causal_conv_silu(int dtype, const void* in, int ld_in, const float* w, const float* bias,
                                  const float* conv_state, void* out, int ld_out, const int* token_seq,
                                  const int* cu_seqlens, const int* slots, int n_tokens, int C, int taps,
-                                 cudaStream_t stream) {
+                                 int n_plain, float* pairs, cudaStream_t stream) {
     if (n_tokens <= 0 || C <= 0) return 0;
-    if (taps < 1 || ld_in < C || ld_out < C || (taps > 1 && conv_state == nullptr)) return kErrBadArgument;
+    if (pairs == nullptr) n_plain = C;
+    if (taps < 1 || ld_in < C || ld_out < n_plain || (taps > 1 && conv_state == nullptr)) return kErrBadArgument;
+    if (n_plain < 0 || n_plain > C || (C - n_plain) % 2) return kErrBadArgument;
     if ((C + 127) / 128 > 65535) return kErrUnsupported;
     if (dtype == 1 && C % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && ((uintptr_t)in % 16) == 0 &&
-        ((uintptr_t)out % 16) == 0 && ((uintptr_t)conv_state % 16) == 0 && ((uintptr_t)w % 16) == 0) {
+        ((uintptr_t)out % 16) == 0 && ((uintptr_t)conv_state % 16) == 0 && ((uintptr_t)w % 16) == 0 &&
+        n_plain % 8 == 0 && (C - n_plain) % 16 == 0) {
         const int per_block = C / 8 < 128 ? (C / 8 + 31) / 32 * 32 : 128;
         const dim3 grid_vec(n_tokens, (C / 8 + per_block - 1) / per_block);
-        return launch_chained(causal_conv_silu_bf16_vec_kernel, grid_vec, dim3(per_block), 0, stream, (const bf16*)in, ld_in, w, bias, conv_state, (bf16*)out, ld_out, token_seq, cu_seqlens, slots, C, taps);
+        return launch_chained(causal_conv_silu_bf16_vec_kernel, grid_vec, dim3(per_block), 0, stream, (const bf16*)in, ld_in, w, bias, conv_state, (bf16*)out, ld_out, token_seq, cu_seqlens, slots, C, taps, n_plain, pairs);
     }
     const dim3 grid(n_tokens, (C + 127) / 128);
-    if (dtype == 0) return launch_chained(causal_conv_silu_kernel<float>, grid, dim3(128), 0, stream, (const float*)in, ld_in, w, bias, conv_state, (float*)out, ld_out, token_seq, cu_seqlens, slots, C, taps);
-    if (dtype == 1) return launch_chained(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)in, ld_in, w, bias, conv_state, (bf16*)out, ld_out, token_seq, cu_seqlens, slots, C, taps);
+    if (dtype == 0) return launch_chained(causal_conv_silu_kernel<float>, grid, dim3(128), 0, stream, (const float*)in, ld_in, w, bias, conv_state, (float*)out, ld_out, token_seq, cu_seqlens, slots, C, taps, n_plain, pairs);
+    if (dtype == 1) return launch_chained(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)in, ld_in, w, bias, conv_state, (bf16*)out, ld_out, token_seq, cu_seqlens, slots, C, taps, n_plain, pairs);
     return kErrBadArgument;
 }
 
 GTG_API int gtg_causal_conv_step(int dtype, const void* in, int ld_in, const float* w, const float* bias,
                                  float* conv_state, void* out, int ld_out, const int* slots, int n_seqs, int C,
-                                 int taps, cudaStream_t stream) {
+                                 int taps, int n_plain, float* pairs, cudaStream_t stream) {
     if (n_seqs <= 0 || C <= 0) return 0;
-    if (taps < 1 || ld_in < C || ld_out < C || (taps > 1 && conv_state == nullptr)) return kErrBadArgument;
+    if (pairs == nullptr) n_plain = C;
+    if (taps < 1 || ld_in < C || ld_out < n_plain || (taps > 1 && conv_state == nullptr)) return kErrBadArgument;
+    if (n_plain < 0 || n_plain > C || (C - n_plain) % 2) return kErrBadArgument;
     if ((C + 127) / 128 > 65535) return kErrUnsupported;
     const dim3 grid(n_seqs, (C + 127) / 128);
-    if (dtype == 0) return launch_chained(causal_conv_step_kernel<float>, grid, dim3(128), 0, stream, (const float*)in, ld_in, w, bias, conv_state, (float*)out, ld_out, slots, C, taps);
-    if (dtype == 1) return launch_chained(causal_conv_step_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)in, ld_in, w, bias, conv_state, (bf16*)out, ld_out, slots, C, taps);
+    if (dtype == 0) return launch_chained(causal_conv_step_kernel<float>, grid, dim3(128), 0, stream, (const float*)in, ld_in, w, bias, conv_state, (float*)out, ld_out, slots, C, taps, n_plain, pairs);
+    if (dtype == 1) return launch_chained(causal_conv_step_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)in, ld_in, w, bias, conv_state, (bf16*)out, ld_out, slots, C, taps, n_plain, pairs);
     return kErrBadArgument;
 }
 
@@ -497,13 +524,15 @@ static int scan_split(int N, int cols) {
     return R;
 }
 
-GTG_API int gtg_ssm_scan(int dtype, const void* xbc, int ld_xbc, const void* dt_raw, int ld_dt,
+GTG_API int gtg_ssm_scan(int dtype, const void* x, int ld_x, const float* bc, int ld_bc, const void* dt_raw, int ld_dt,
                          const float* dt_bias, const float* a_log, const float* skip, float* state,
                          float* y, int ld_y, const int* cu_seqlens, const int* slots, int n_seqs,
                          int heads, int groups, int N, int P, int one_token_each, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0) return kErrBadArgument;
+    if (ld_x < heads * P || ld_bc < groups * N || ((uintptr_t)bc % 8)) return kErrBadArgument;
     if (n_seqs > 65535) return kErrUnsupported;
+    const float2* pairs = (const float2*)bc;
     if (one_token_each && P % 4 == 0 && P <= 1024 && ((uintptr_t)state % 16) == 0) {
         const int P4 = P / 4;
         int J = 256 / P4;
@@ -514,8 +543,8 @@ GTG_API int gtg_ssm_scan(int dtype, const void* xbc, int ld_xbc, const void* dt_
         const size_t smem_step = (size_t)(2 * N + J * P) * sizeof(float);
         if (threads <= 1024 && smem_step <= 48 * 1024) {
             const dim3 grid_step(heads, n_seqs);
-            if (dtype == 0) return launch_chained(ssm_step_kernel<float>, grid_step, dim3(threads), smem_step, stream, (const float*)xbc, ld_xbc, (const float*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, slots, heads, groups, N, P, J);
-            if (dtype == 1) return launch_chained(ssm_step_kernel<bf16>, grid_step, dim3(threads), smem_step, stream, (const bf16*)xbc, ld_xbc, (const bf16*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, slots, heads, groups, N, P, J);
+            if (dtype == 0) return launch_chained(ssm_step_kernel<float>, grid_step, dim3(threads), smem_step, stream, (const float*)x, ld_x, pairs, ld_bc, (const float*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, slots, heads, groups, N, P, J);
+            if (dtype == 1) return launch_chained(ssm_step_kernel<bf16>, grid_step, dim3(threads), smem_step, stream, (const bf16*)x, ld_x, pairs, ld_bc, (const bf16*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, slots, heads, groups, N, P, J);
             return kErrBadArgument;
         }
     }
@@ -526,11 +555,12 @@ GTG_API int gtg_ssm_scan(int dtype, const void* xbc, int ld_xbc, const void* dt_
             n_sm = 148;
     }
     // Slices of columns, so that a few long sequences still give about three blocks per
-    // multiprocessor.  Where every run of x, B and C starts on a 16-byte boundary the
-    // slices are halves, quarters, ... of a head that keep that alignment and the rows
+    // multiprocessor.  Where every run of x and of the pairs starts on a 16-byte boundary
+    // the slices are halves, quarters, ... of a head that keep that alignment and the rows
     // come by asynchronous copies; otherwise slices of at least four columns, read plainly.
     const int vec = dtype == 0 ? 4 : 8;
-    const bool aligned = N % vec == 0 && P % vec == 0 && ld_xbc % vec == 0 && ((uintptr_t)xbc % 16) == 0;
+    const bool aligned = N % 2 == 0 && ld_bc % 2 == 0 && ((uintptr_t)bc % 16) == 0 &&
+                         P % vec == 0 && ld_x % vec == 0 && ((uintptr_t)x % 16) == 0;
     int PS = P;
     if (aligned) {
         while ((long long)heads * n_seqs * (P / PS) < 3LL * n_sm && PS % 2 == 0 && (PS / 2) % vec == 0) PS /= 2;
@@ -541,26 +571,38 @@ GTG_API int gtg_ssm_scan(int dtype, const void* xbc, int ld_xbc, const void* dt_
         PS = (P + slices - 1) / slices;
     }
     const int slices = (P + PS - 1) / PS;
-    const int R = scan_split(N, PS);
+    int R = scan_split(N, PS);
     if ((N + R - 1) / R > kRowsPerThread) return kErrUnsupported;
+    // few warps on the device in all: halve the rows of a thread, which doubles them
+    if (N == R * 16 && R < 32 && (long long)heads * n_seqs * P * R / 32 < 8LL * n_sm) R *= 2;
     const int threads = (PS * R + 31) / 32 * 32;
     if (threads > 1024) return kErrUnsupported;
-    size_t smem = (size_t)(kTile * (PS + 2 * N) + 2 * kTile) * sizeof(float);
-    if (aligned) smem += (size_t)2 * kTile * (2 * N + PS) * (dtype == 0 ? 4 : 2);
+    size_t smem = (size_t)(4 * kTile * N + kTile * PS + 1 + 2 * kTile) * sizeof(float);
+    if (aligned) smem += (size_t)2 * kTile * PS * (dtype == 0 ? 4 : 2);
     if (smem > 200 * 1024) return kErrUnsupported;
     const dim3 grid(heads, n_seqs, slices);
     cudaError_t e;
     const int rows = (N + R - 1) / R;
-#define GTG_SCAN_LAUNCH_KR(T, ASYNC, KR)                                                                                 \
+#define GTG_SCAN_LAUNCH_KR(T, ASYNC, KR, RT)                                                                             \
     do {                                                                                                                 \
-        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(ssm_scan_kernel<T, ASYNC, KR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e; \
-        return launch_chained(ssm_scan_kernel<T, ASYNC, KR>, grid, dim3(threads), smem, stream, (const T*)xbc, ld_xbc, (const T*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, cu_seqlens, slots, heads, groups, N, P, R, PS); \
+        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(ssm_scan_kernel<T, ASYNC, KR, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e; \
+        return launch_chained(ssm_scan_kernel<T, ASYNC, KR, RT>, grid, dim3(threads), smem, stream, (const T*)x, ld_x, pairs, ld_bc, (const T*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, cu_seqlens, slots, heads, groups, N, P, R, PS); \
     } while (0)
 #define GTG_SCAN_LAUNCH(T, ASYNC)                                                                                        \
     do {                                                                                                                 \
-        if (rows <= 4) GTG_SCAN_LAUNCH_KR(T, ASYNC, 4);                                                                  \
-        if (rows <= 8) GTG_SCAN_LAUNCH_KR(T, ASYNC, 8);                                                                  \
-        GTG_SCAN_LAUNCH_KR(T, ASYNC, 16);                                                                                \
+        if (ASYNC && N == R * 16) {              /* the usual state sizes: R and N constants of the kernel */            \
+            if (R == 2) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 2);                                                             \
+            if (R == 4) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 4);                                                             \
+            if (R == 8) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 8);                                                             \
+        }                                                                                                                \
+        if (ASYNC && N == R * 8) {                                                                                       \
+            if (R == 4) GTG_SCAN_LAUNCH_KR(T, ASYNC, 8, 4);                                                              \
+            if (R == 8) GTG_SCAN_LAUNCH_KR(T, ASYNC, 8, 8);                                                              \
+            if (R == 16) GTG_SCAN_LAUNCH_KR(T, ASYNC, 8, 16);                                                            \
+        }                                                                                                                \
+        if (rows <= 4) GTG_SCAN_LAUNCH_KR(T, ASYNC, 4, 0);                                                               \
+        if (rows <= 8) GTG_SCAN_LAUNCH_KR(T, ASYNC, 8, 0);                                                               \
+        GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 0);                                                                             \
     } while (0)
     if (dtype == 0) { if (aligned) GTG_SCAN_LAUNCH(float, true); else GTG_SCAN_LAUNCH(float, false); }
     if (dtype == 1) { if (aligned) GTG_SCAN_LAUNCH(bf16, true); else GTG_SCAN_LAUNCH(bf16, false); }

@@ -30,10 +30,10 @@ _SIGNATURES = {
     "gtg_activation": ("elementwise", [_I, _P, _I, _I, _I, _I, _P]),
     "gtg_softcap": ("elementwise", [_P, _L, _F, _P]),
     "gtg_hidden_concat": ("elementwise", [_I, _P, _P, _P, _P, _I, _I, _P]),
-    "gtg_causal_conv_silu": ("ssm", [_I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _P]),
+    "gtg_causal_conv_silu": ("ssm", [_I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "gtg_conv_state_update": ("ssm", [_I, _P, _I, _P, _P, _P, _I, _I, _I, _P]),
-    "gtg_ssm_scan": ("ssm", [_I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
-    "gtg_causal_conv_step": ("ssm", [_I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _P]),
+    "gtg_ssm_scan": ("ssm", [_I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "gtg_causal_conv_step": ("ssm", [_I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _P]),
     "gtg_gated_rmsnorm": ("ssm", [_I, _P, _I, _P, _I, _P, _F, _P, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_simt": ("gemm_f32", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_advance": ("elementwise", [_P, _P, _P, _P, _I, _P]),
@@ -397,17 +397,26 @@ def _int32(name: str, *tensors) -> None:
 
 def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                      conv_state: torch.Tensor, out: torch.Tensor, token_seq, cu_seqlens, slots,
-                     n_seqs: Optional[int] = None, update_state: bool = False, one_token_each: bool = False) -> None:
+                     n_seqs: Optional[int] = None, update_state: bool = False, one_token_each: bool = False,
+                     pairs: Optional[torch.Tensor] = None) -> None:
     """out[n, c] = silu(bias[c] + sum_j weight[j, c] x[n - (taps-1-j), c]) (weight is
     held tap by tap, [taps, C]; the last tap is the current token's) within each
     sequence of the packed rows; what precedes a sequence's first row of the step
     comes from conv_state[slot] ([taps-1, C] float32, oldest first).  With
     `update_state` the state is then left as `conv_state_update` leaves it (one
-    kernel does both when every sequence brings one token: `one_token_each`)."""
+    kernel does both when every sequence brings one token: `one_token_each`).
+    With `pairs` (float32 [n, Q, 2]) only the first C - 2Q channels go to `out`;
+    the rest, two runs U and V of Q channels, are left as float (U_q, V_q) side
+    by side, which is how `ssm_scan` reads a recurrence's B and C."""
     _rows2d(x, "causal_conv_silu: x"); _rows2d(out, "causal_conv_silu: out")
     n, C = x.shape
     taps = weight.shape[0]
-    _need(out.dtype == x.dtype and tuple(out.shape) == (n, C), "causal_conv_silu: out must match x")
+    n_plain = C
+    if pairs is not None:
+        _need(pairs.dtype == torch.float32 and pairs.is_contiguous() and pairs.dim() == 3 and pairs.shape[0] == n
+              and pairs.shape[2] == 2 and 2 * pairs.shape[1] <= C, "causal_conv_silu: pairs must be float32 [n, Q, 2]")
+        n_plain = C - 2 * pairs.shape[1]
+    _need(out.dtype == x.dtype and tuple(out.shape) == (n, n_plain), "causal_conv_silu: out must be [n, plain channels] of x's dtype")
     _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.dim() == 2 and weight.shape[1] == C,
           "causal_conv_silu: weight must be float32 [taps, C]")
     _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C),
@@ -418,12 +427,12 @@ def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch
     if update_state and one_token_each:
         _need(n == slots.numel(), "causal_conv_silu: one token each means as many rows as sequences")
         _check(_fn("gtg_causal_conv_step")(_dt(x), _ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(conv_state),
-                                           _ptr(out), out.stride(0), _ptr(slots), n, C, taps, _stream()),
+                                           _ptr(out), out.stride(0), _ptr(slots), n, C, taps, n_plain, _ptr(pairs), _stream()),
                "causal_conv_silu(step)")
         return
     _check(_fn("gtg_causal_conv_silu")(_dt(x), _ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(conv_state),
                                        _ptr(out), out.stride(0), _ptr(token_seq), _ptr(cu_seqlens), _ptr(slots),
-                                       n, C, taps, _stream()), "causal_conv_silu")
+                                       n, C, taps, n_plain, _ptr(pairs), _stream()), "causal_conv_silu")
     if update_state:
         conv_state_update(x, conv_state, cu_seqlens, slots, slots.numel() if n_seqs is None else n_seqs)
 
@@ -440,30 +449,32 @@ def conv_state_update(x: torch.Tensor, conv_state: torch.Tensor, cu_seqlens, slo
                                         int(n_seqs), C, keep + 1, _stream()), "conv_state_update")
 
 
-def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+def ssm_scan(x: torch.Tensor, bc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
              skip: torch.Tensor, state: torch.Tensor, y: torch.Tensor, cu_seqlens, slots, n_seqs: int,
              heads: int, groups: int, n_state: int, head_dim: int, one_token_each: bool = False) -> None:
     """The state-space recurrence with a scalar decay per head, token by token:
-    xbc [n, heads*P + 2*groups*N] = [x | B | C] per row, dt_raw [n, heads];
-    dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T,
+    x [n, heads*P]; bc float32 [n, groups*N, 2], (B_n, C_n) side by side;
+    dt_raw [n, heads]; dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T,
     y = S^T C + skip * x.  state: float32 [slots, heads, N, P], read and left
     per sequence; y: float32 [n, heads*P].  `one_token_each`: row b is sequence
     b's only token (a decode step), which a kernel of its own serves."""
-    _rows2d(xbc, "ssm_scan: xbc"); _rows2d(dt_raw, "ssm_scan: dt_raw"); _rows2d(y, "ssm_scan: y")
-    n = xbc.shape[0]
+    _rows2d(x, "ssm_scan: x"); _rows2d(dt_raw, "ssm_scan: dt_raw"); _rows2d(y, "ssm_scan: y")
+    n = x.shape[0]
     inner = heads * head_dim
-    _need(xbc.shape[1] == inner + 2 * groups * n_state and dt_raw.dtype == xbc.dtype and tuple(dt_raw.shape) == (n, heads),
-          "ssm_scan: xbc must be [n, heads*P + 2*groups*N] and dt_raw [n, heads] of one dtype")
+    _need(x.shape[1] == inner and dt_raw.dtype == x.dtype and tuple(dt_raw.shape) == (n, heads),
+          "ssm_scan: x must be [n, heads*P] and dt_raw [n, heads] of one dtype")
+    _need(bc.dtype == torch.float32 and bc.is_contiguous() and tuple(bc.shape) == (n, groups * n_state, 2),
+          "ssm_scan: bc must be contiguous float32 [n, groups*N, 2]")
     _need(y.dtype == torch.float32 and tuple(y.shape) == (n, inner), "ssm_scan: y must be float32 [n, heads*P]")
     for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("skip", skip)):
         _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == heads, f"ssm_scan: {name} must be float32 [heads]")
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, n_state, head_dim),
           "ssm_scan: state must be float32 [slots, heads, N, P]")
     _int32("ssm_scan", cu_seqlens, slots)
-    _check(_fn("gtg_ssm_scan")(_dt(xbc), _ptr(xbc), xbc.stride(0), _ptr(dt_raw), dt_raw.stride(0), _ptr(dt_bias),
-                               _ptr(a_log), _ptr(skip), _ptr(state), _ptr(y), y.stride(0), _ptr(cu_seqlens), _ptr(slots),
-                               int(n_seqs), heads, groups, n_state, head_dim, 1 if one_token_each and n == n_seqs else 0,
-                               _stream()), "ssm_scan")
+    _check(_fn("gtg_ssm_scan")(_dt(x), _ptr(x), x.stride(0), _ptr(bc), groups * n_state, _ptr(dt_raw), dt_raw.stride(0),
+                               _ptr(dt_bias), _ptr(a_log), _ptr(skip), _ptr(state), _ptr(y), y.stride(0),
+                               _ptr(cu_seqlens), _ptr(slots), int(n_seqs), heads, groups, n_state, head_dim,
+                               1 if one_token_each and n == n_seqs else 0, _stream()), "ssm_scan")
 
 
 def gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,

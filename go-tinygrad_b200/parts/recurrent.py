@@ -17,8 +17,8 @@ conv_taps - 1 inputs of the convolution; both live in the cache as
 `StateRequest`s, are zero when a slot is opened, and are read and left by
 every step, so a prompt, a portion of one and a single token are one code path.
 Step sizes, decays, the state, the recurrence's sums and the norm are float32
-in both compute dtypes; projections and the convolution's result are in the
-compute dtype.  The reference has no recurrent mixer.
+in both compute dtypes, and so are B and C from the convolution on; the
+projections and the x the convolution leaves are in the compute dtype.  The reference has no recurrent mixer.
 
 Parameters: ``hidden_size``, ``n_heads``, ``head_dim``, ``state_size``,
 ``n_groups``, ``conv_taps``, ``norm_parts``, ``eps`` and the tensor names
@@ -99,13 +99,15 @@ class Mamba2(Mixer):
         conv_in = proj[:, self.inner: self.inner + self.conv_dim]
         dt_raw = proj[:, self.inner + self.conv_dim:]
         conv_state, ssm_state = cache.state("conv"), cache.state("ssm")
-        xbc = rt.empty(n, self.conv_dim)
-        ops.causal_conv_silu(conv_in, self.conv_w, self.conv_b, conv_state, xbc,
+        # x in the compute dtype; B and C as float pairs, the form the recurrence reads
+        xs = rt.empty(n, self.inner)
+        bc = rt.empty(n, self.n_groups * self.n_state, 2, dtype=torch.float32)
+        ops.causal_conv_silu(conv_in, self.conv_w, self.conv_b, conv_state, xs,
                              ctx.token_seq, ctx.cu_seqlens, ctx.slots, n_seqs=ctx.n_seqs, update_state=True,
-                             one_token_each=ctx.is_decode)
-        ctx.trace("conv", xbc)
+                             one_token_each=ctx.is_decode, pairs=bc)
+        ctx.trace("conv", xs)
         y = rt.empty(n, self.inner, dtype=torch.float32)
-        ops.ssm_scan(xbc, dt_raw, self.dt_bias, self.a_log, self.d, ssm_state, y, ctx.cu_seqlens, ctx.slots,
+        ops.ssm_scan(xs, bc, dt_raw, self.dt_bias, self.a_log, self.d, ssm_state, y, ctx.cu_seqlens, ctx.slots,
                      ctx.n_seqs, self.n_heads, self.n_groups, self.n_state, self.head_dim,
                      one_token_each=ctx.is_decode)
         ctx.trace("scan", y)

@@ -196,6 +196,17 @@ def test_convolution_carries_its_last_inputs_across_portions(dtype):
             at += n
         lim = 1e-5 if dtype == "float32" else 1e-2
         assert np.abs(got.float().cpu().numpy() - want).max() <= lim * max(1.0, np.abs(want).max())
+        if C % 4 == 0:                                     # the last half of the channels as float pairs (U_q, V_q)
+            q, n_all = C // 4, 2 * T
+            plain_out = torch.empty(n_all, C - 2 * q, dtype=TORCH[dtype], device=DEV)
+            pairs = torch.empty(n_all, q, 2, device=DEV)
+            fresh = torch.zeros(5, max(taps - 1, 0), C, device=DEV)
+            ops.causal_conv_silu(x, t32(w.T.copy()), t32(b), fresh, plain_out, i32([0] * T + [1] * T), i32([0, T, 2 * T]),
+                                 i32([3, 0]), pairs=pairs)
+            got_pairs = pairs.cpu().numpy()
+            assert np.abs(plain_out.float().cpu().numpy() - want[:, :C - 2 * q]).max() <= lim * max(1.0, np.abs(want).max())
+            assert np.abs(got_pairs[:, :, 0] - want[:, C - 2 * q:C - q]).max() <= 1e-5 * max(1.0, np.abs(want).max())
+            assert np.abs(got_pairs[:, :, 1] - want[:, C - q:]).max() <= 1e-5 * max(1.0, np.abs(want).max())
         if taps > 1:
             np.testing.assert_array_equal(state[3].cpu().numpy(), xs[T - taps + 1:T])
             np.testing.assert_array_equal(state[0].cpu().numpy(), xs[2 * T - taps + 1:])
@@ -224,6 +235,8 @@ def test_recurrence_keeps_its_state_across_portions_and_remembers_far_tokens(dty
                                   xs[1:, inner:inner + groups * N].reshape(T - 1, groups, N),
                                   xs[1:, inner + groups * N:].reshape(T - 1, groups, N), skip).reshape(T - 1, inner)
     assert np.abs(want[-1, :P] - forgot[-1, :P]).max() > 0.05 * np.abs(want[-1, :P]).max()   # the test can see token 0
+    x_in = xbc[:, :inner].contiguous()
+    bc_in = torch.stack([xbc[:, inner:inner + groups * N], xbc[:, inner + groups * N:]], dim=2).float().contiguous()
     for portions in ([T], [1], [15, 16, 17, 1, 2, 33], [100, 1]):
         state = torch.zeros(3, heads, N, P, device=DEV)
         got = torch.zeros(T, inner, device=DEV)
@@ -231,7 +244,7 @@ def test_recurrence_keeps_its_state_across_portions_and_remembers_far_tokens(dty
         while at < T:
             n = min(portions[min(i, len(portions) - 1)], T - at)
             y = torch.empty(n, inner, device=DEV)
-            ops.ssm_scan(xbc[at:at + n], dt_raw[at:at + n], t32(dt_bias), t32(a_log), t32(skip), state, y,
+            ops.ssm_scan(x_in[at:at + n], bc_in[at:at + n], dt_raw[at:at + n], t32(dt_bias), t32(a_log), t32(skip), state, y,
                          i32([0, n]), i32([2]), 1, heads, groups, N, P, one_token_each=(n == 1 and portions != [1]))
             got[at:at + n] = y
             at += n
