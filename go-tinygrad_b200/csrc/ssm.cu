@@ -187,7 +187,8 @@ __device__ __forceinline__ void copy_async_wait_all_but_one() { asm volatile("cp
 // KR: rows of S a thread owns (R * KR >= N; the rows beyond N, if any, are skipped).
 // RT: R known when compiling, with N = RT * KR (every offset into the staged pairs
 // is then a constant), or 0: R and N as passed.
-template <typename T, bool kAsync, int KR, int RT>
+// CP: neighbouring columns of S a thread owns (the pairs it reads serve all of them).
+template <typename T, bool kAsync, int KR, int RT, int CP>
 __global__ void ssm_scan_kernel(const T* __restrict__ x, int ld_x, const float2* __restrict__ bc, int ld_bc,
                                 const T* __restrict__ dt_raw, int ld_dt,
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
@@ -207,16 +208,18 @@ __global__ void ssm_scan_kernel(const T* __restrict__ x, int ld_x, const float2*
     const int cols = min(PS, P - p0);
     const int g = h / (heads / groups);
     const int tid = threadIdx.x;
-    const int pl = tid / R, r = tid - pl * R;
-    const bool owner = pl < cols;
+    const int pg = tid / R, r = tid - pg * R;
+    const int pl = pg * CP;                                  // the thread's first column within the slice
+    const bool owner = pl < cols;                            // (with CP > 1 a slice's columns are a multiple of CP)
     const int p = p0 + pl;
     const int first = cu_seqlens[b], last = cu_seqlens[b + 1];
     float* S = state + ((size_t)slots[b] * heads + h) * N * P;
-    float s[KR];
+    float s[CP][KR];
 #pragma unroll
     for (int k = 0; k < KR; ++k) {
         const int n = r + R * k;
-        s[k] = (owner && n < N) ? S[(size_t)n * P + p] : 0.f;
+#pragma unroll
+        for (int c = 0; c < CP; ++c) s[c][k] = (owner && n < N) ? S[(size_t)n * P + p + c] : 0.f;
     }
     const float bias = dt_bias[h], rate = expf(a_log[h]), d_skip = skip[h];
     const bool exact = RT != 0 || R * KR == N;               // no row of a thread lies beyond N
@@ -225,12 +228,14 @@ __global__ void ssm_scan_kernel(const T* __restrict__ x, int ld_x, const float2*
     auto fetch = [&](int t0, int stage) {
         if (t0 < last) {
             const int nt = min(kTile, last - t0);
-            const int nv = N / 2, xv = PS / kVec, per_row = nv + xv;
-            for (int v = tid; v < nt * per_row; v += blockDim.x) {
-                const int tt = v / per_row, j = v - tt * per_row;
-                if (j < nv) copy_async_16(sBC + (stage * kTile + tt) * N + 2 * j, bc + (size_t)(t0 + tt) * ld_bc + g * N + 2 * j);
-                else copy_async_16(rawx + (stage * kTile + tt) * PS + (j - nv) * kVec,
-                                   x + (size_t)(t0 + tt) * ld_x + h * P + p0 + (j - nv) * kVec);
+            const int nv = N / 2, xv = PS / kVec;            // 16-byte pieces of a row of pairs, of a row of x
+            for (int v = tid; v < nt * nv; v += blockDim.x) {
+                const int tt = v / nv, j = v - tt * nv;      // nv is a constant power of two where RT is set
+                copy_async_16(sBC + (stage * kTile + tt) * N + 2 * j, bc + (size_t)(t0 + tt) * ld_bc + g * N + 2 * j);
+            }
+            for (int v = tid; v < nt * xv; v += blockDim.x) {
+                const int tt = v / xv, j = v - tt * xv;
+                copy_async_16(rawx + (stage * kTile + tt) * PS + j * kVec, x + (size_t)(t0 + tt) * ld_x + h * P + p0 + j * kVec);
             }
         }
         copy_async_commit();
@@ -266,18 +271,21 @@ __global__ void ssm_scan_kernel(const T* __restrict__ x, int ld_x, const float2*
         if (tid < kTile && t0 + kTile + tid < last) dt_next = to_f32<T>(dt_raw[(size_t)(t0 + kTile + tid) * ld_dt + h]);
         const float2* tile_bc = sBC + stage * kTile * N + r;
         for (int tq = 0; tq < nt; tq += 4) {
-            float acc[4], xs[4];
+            float acc[4][CP], xs[4][CP];
             if (exact && tq + 4 <= nt) {
-                // four whole tokens, no branch in the way: the rows' chains (one per k) run side
-                // by side, each stepping through the four tokens in order
-                float da_a[4], dx[4];
+                // four whole tokens, no branch in the way: the rows' chains (one per k and column) run
+                // side by side, each stepping through the four tokens in order
+                float da_a[4], dx[4][CP];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const float2 da = sda[tq + u];
-                    xs[u] = owner ? sx[(tq + u) * PS + pl] : 0.f;
                     da_a[u] = da.y;
-                    dx[u] = da.x * xs[u];
-                    acc[u] = 0.f;
+#pragma unroll
+                    for (int c = 0; c < CP; ++c) {
+                        xs[u][c] = owner ? sx[(tq + u) * PS + pl + c] : 0.f;
+                        dx[u][c] = da.x * xs[u][c];
+                        acc[u][c] = 0.f;
+                    }
                 }
                 const float2* row = tile_bc + tq * N;
 #pragma unroll
@@ -285,27 +293,37 @@ __global__ void ssm_scan_kernel(const T* __restrict__ x, int ld_x, const float2*
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const float2 v = row[u * N + R * k];
-                        s[k] = fmaf(da_a[u], s[k], v.x * dx[u]);
-                        acc[u] = fmaf(s[k], v.y, acc[u]);
+#pragma unroll
+                        for (int c = 0; c < CP; ++c) {
+                            s[c][k] = fmaf(da_a[u], s[c][k], v.x * dx[u][c]);
+                            acc[u][c] = fmaf(s[c][k], v.y, acc[u][c]);
+                        }
                     }
                 }
             } else {
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int tt = tq + u;
-                    acc[u] = 0.f;
-                    xs[u] = 0.f;
+#pragma unroll
+                    for (int c = 0; c < CP; ++c) { acc[u][c] = 0.f; xs[u][c] = 0.f; }
                     if (tt < nt) {
                         const float2 da = sda[tt];
-                        xs[u] = owner ? sx[tt * PS + pl] : 0.f;
-                        const float dx = da.x * xs[u];
+                        float dx[CP];
+#pragma unroll
+                        for (int c = 0; c < CP; ++c) {
+                            xs[u][c] = owner ? sx[tt * PS + pl + c] : 0.f;
+                            dx[c] = da.x * xs[u][c];
+                        }
                         const float2* row = tile_bc + tt * N;
 #pragma unroll
                         for (int k = 0; k < KR; ++k) {
                             if (r + R * k < N) {
                                 const float2 v = row[R * k];
-                                s[k] = fmaf(da.y, s[k], v.x * dx);
-                                acc[u] = fmaf(s[k], v.y, acc[u]);
+#pragma unroll
+                                for (int c = 0; c < CP; ++c) {
+                                    s[c][k] = fmaf(da.y, s[c][k], v.x * dx[c]);
+                                    acc[u][c] = fmaf(s[c][k], v.y, acc[u][c]);
+                                }
                             }
                         }
                     }
@@ -313,12 +331,18 @@ __global__ void ssm_scan_kernel(const T* __restrict__ x, int ld_x, const float2*
             }
             for (int o = R >> 1; o > 0; o >>= 1) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int c = 0; c < CP; ++c) acc[u][c] += __shfl_xor_sync(0xffffffffu, acc[u][c], o);
             }
             if (owner && r == 0) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
-                    if (tq + u < nt) y[(size_t)(t0 + tq + u) * ld_y + h * P + p] = fmaf(d_skip, xs[u], acc[u]);
+                    if (tq + u < nt) {
+#pragma unroll
+                        for (int c = 0; c < CP; ++c)
+                            y[(size_t)(t0 + tq + u) * ld_y + h * P + p + c] = fmaf(d_skip, xs[u][c], acc[u][c]);
+                    }
             }
         }
     }
@@ -327,7 +351,10 @@ __global__ void ssm_scan_kernel(const T* __restrict__ x, int ld_x, const float2*
 #pragma unroll
         for (int k = 0; k < KR; ++k) {
             const int n = r + R * k;
-            if (n < N) S[(size_t)n * P + p] = s[k];
+            if (n < N) {
+#pragma unroll
+                for (int c = 0; c < CP; ++c) S[(size_t)n * P + p + c] = s[c][k];
+            }
         }
     }
 }
@@ -554,8 +581,10 @@ GTG_API int gtg_ssm_scan(int dtype, const void* x, int ld_x, const float* bc, in
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
             n_sm = 148;
     }
-    // Slices of columns, so that a few long sequences still give about three blocks per
-    // multiprocessor.  Where every run of x and of the pairs starts on a 16-byte boundary
+    // Slices of columns, so that a few long sequences still give a block to most
+    // multiprocessors (measured at 64 heads of 64 columns and a state of 128: two slices
+    // of 32 columns, 128 blocks, 0.46 ms for 2,048 tokens; four slices 0.49, eight 0.55:
+    // every slice stages the head's B and C again).  Where every run of x and of the pairs starts on a 16-byte boundary
     // the slices are halves, quarters, ... of a head that keep that alignment and the rows
     // come by asynchronous copies; otherwise slices of at least four columns, read plainly.
     const int vec = dtype == 0 ? 4 : 8;
@@ -563,9 +592,9 @@ GTG_API int gtg_ssm_scan(int dtype, const void* x, int ld_x, const float* bc, in
                          P % vec == 0 && ld_x % vec == 0 && ((uintptr_t)x % 16) == 0;
     int PS = P;
     if (aligned) {
-        while ((long long)heads * n_seqs * (P / PS) < 3LL * n_sm && PS % 2 == 0 && (PS / 2) % vec == 0) PS /= 2;
+        while (2LL * heads * n_seqs * (P / PS) <= (long long)n_sm && PS % 2 == 0 && (PS / 2) % vec == 0) PS /= 2;
     } else {
-        int slices = (3 * n_sm + heads * n_seqs - 1) / (heads * n_seqs);
+        int slices = (n_sm + heads * n_seqs - 1) / (heads * n_seqs);
         if (slices > (P + 3) / 4) slices = (P + 3) / 4;
         if (slices < 1) slices = 1;
         PS = (P + slices - 1) / slices;
@@ -573,8 +602,6 @@ GTG_API int gtg_ssm_scan(int dtype, const void* x, int ld_x, const float* bc, in
     const int slices = (P + PS - 1) / PS;
     int R = scan_split(N, PS);
     if ((N + R - 1) / R > kRowsPerThread) return kErrUnsupported;
-    // few warps on the device in all: halve the rows of a thread, which doubles them
-    if (N == R * 16 && R < 32 && (long long)heads * n_seqs * P * R / 32 < 8LL * n_sm) R *= 2;
     const int threads = (PS * R + 31) / 32 * 32;
     if (threads > 1024) return kErrUnsupported;
     size_t smem = (size_t)(4 * kTile * N + kTile * PS + 1 + 2 * kTile) * sizeof(float);
@@ -583,26 +610,22 @@ GTG_API int gtg_ssm_scan(int dtype, const void* x, int ld_x, const float* bc, in
     const dim3 grid(heads, n_seqs, slices);
     cudaError_t e;
     const int rows = (N + R - 1) / R;
-#define GTG_SCAN_LAUNCH_KR(T, ASYNC, KR, RT)                                                                             \
+#define GTG_SCAN_LAUNCH_KR(T, ASYNC, KR, RT, CP)                                                                         \
     do {                                                                                                                 \
-        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(ssm_scan_kernel<T, ASYNC, KR, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e; \
-        return launch_chained(ssm_scan_kernel<T, ASYNC, KR, RT>, grid, dim3(threads), smem, stream, (const T*)x, ld_x, pairs, ld_bc, (const T*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, cu_seqlens, slots, heads, groups, N, P, R, PS); \
+        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(ssm_scan_kernel<T, ASYNC, KR, RT, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e; \
+        return launch_chained(ssm_scan_kernel<T, ASYNC, KR, RT, CP>, grid, dim3(((PS / CP) * R + 31) / 32 * 32), smem, stream, (const T*)x, ld_x, pairs, ld_bc, (const T*)dt_raw, ld_dt, dt_bias, a_log, skip, state, y, ld_y, cu_seqlens, slots, heads, groups, N, P, R, PS); \
     } while (0)
 #define GTG_SCAN_LAUNCH(T, ASYNC)                                                                                        \
     do {                                                                                                                 \
         if (ASYNC && N == R * 16) {              /* the usual state sizes: R and N constants of the kernel */            \
-            if (R == 2) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 2);                                                             \
-            if (R == 4) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 4);                                                             \
-            if (R == 8) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 8);                                                             \
+            if (R == 2) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 2, 2);                                                          \
+            if (R == 4) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 4, 2);                                                          \
+            if (R == 8) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 8, 2);                                                          \
+            if (R == 16) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 16, 2);                                                        \
         }                                                                                                                \
-        if (ASYNC && N == R * 8) {                                                                                       \
-            if (R == 4) GTG_SCAN_LAUNCH_KR(T, ASYNC, 8, 4);                                                              \
-            if (R == 8) GTG_SCAN_LAUNCH_KR(T, ASYNC, 8, 8);                                                              \
-            if (R == 16) GTG_SCAN_LAUNCH_KR(T, ASYNC, 8, 16);                                                            \
-        }                                                                                                                \
-        if (rows <= 4) GTG_SCAN_LAUNCH_KR(T, ASYNC, 4, 0);                                                               \
-        if (rows <= 8) GTG_SCAN_LAUNCH_KR(T, ASYNC, 8, 0);                                                               \
-        GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 0);                                                                             \
+        if (rows <= 4) GTG_SCAN_LAUNCH_KR(T, ASYNC, 4, 0, 1);                                                            \
+        if (rows <= 8) GTG_SCAN_LAUNCH_KR(T, ASYNC, 8, 0, 1);                                                            \
+        GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 0, 1);                                                                          \
     } while (0)
     if (dtype == 0) { if (aligned) GTG_SCAN_LAUNCH(float, true); else GTG_SCAN_LAUNCH(float, false); }
     if (dtype == 1) { if (aligned) GTG_SCAN_LAUNCH(bf16, true); else GTG_SCAN_LAUNCH(bf16, false); }

@@ -382,10 +382,21 @@ def test_linear_does_not_add_to_a_residual_stream_what_it_cannot_serve():
         assert torch.equal(residual, before)
 
 
-def test_linear_refuses_unaligned_inner_size():
+def test_linear_serves_an_unaligned_inner_size_the_plain_way_and_refuses_it_to_a_named_kernel():
+    """An inner size or a row stride that is no multiple of 8 cannot go through the
+    tensor-core products: the plain walk (float accumulation) takes it; asked for
+    by name, a tensor-core kind still refuses."""
+    for M, N, K in ((4, 5, 12), (150, 37, 21), (3, 9, 7)):
+        x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
+        want = x.float() @ w.float().t()
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+            ops.linear(x, w, out)
+            torch.testing.assert_close(out.float(), want.to(out_dtype).float(), rtol=1e-5 if out_dtype == torch.float32 else 1e-2,
+                                       atol=1e-5 if out_dtype == torch.float32 else 1e-2)
     x, w = rnd(4, 12, dtype=torch.bfloat16), rnd(5, 12, dtype=torch.bfloat16)
     with pytest.raises(ops.KernelError, match="multiples of 8"):
-        ops.linear(x, w, torch.empty(4, 5, dtype=torch.bfloat16, device=DEV))
+        ops.linear(x, w, torch.empty(4, 5, dtype=torch.bfloat16, device=DEV), kind="skinny")
 
 
 # ------------------------------------------------------------------- attention
