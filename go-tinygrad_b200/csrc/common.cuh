@@ -72,6 +72,18 @@ struct KVPages {
     int table_stride;        // entries per slot
 };
 
+// Pointwise activations, evaluated in float.  kind 0: relu(x)^2; 1: gelu in its tanh
+// form, 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))); 2: silu, x / (1 + exp(-x)).
+__device__ __forceinline__ float activate(float x, int kind) {
+    if (kind == 0) { const float r = fmaxf(x, 0.f); return r * r; }
+    if (kind == 1) return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    return x / (1.0f + expf(-x));
+}
+// Epilogue codes of the matrix products from this value on: the plain product with
+// activation (code - kEpiActivation) applied to its float sums before they are rounded.
+constexpr int kEpiActivation = 16;
+constexpr int kActivations = 3;
+
 static inline int launch_status() {
     return (int)cudaGetLastError();
 }

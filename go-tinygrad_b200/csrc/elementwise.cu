@@ -572,12 +572,6 @@ GTG_API int gtg_add_layernorm(int dtype, float* residual, const void* pending, c
 // ------------------------------------------------------ pointwise activations
 // x <- f(x) in place, evaluated in float.  kind 0: relu(x)^2; 1: gelu in its tanh
 // form, 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))); 2: silu, x / (1 + exp(-x)).
-__device__ __forceinline__ float activate(float x, int kind) {
-    if (kind == 0) { const float r = fmaxf(x, 0.f); return r * r; }
-    if (kind == 1) return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
-    return x / (1.0f + expf(-x));
-}
-
 template <typename T>
 __global__ void activation_kernel(T* __restrict__ x, int ld, int M, int I, int kind) {
     chain_release();

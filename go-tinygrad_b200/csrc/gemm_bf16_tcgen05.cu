@@ -159,7 +159,10 @@ template <typename OutT, bool kTest>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_c, int use_store_map,
-                    OutT* __restrict__ C, int ldc, int M, int N, int K, int epi, RopeKV rope) {
+                    OutT* __restrict__ C, int ldc, int M, int N, int K, int epi_code, RopeKV rope) {
+    // a code from kEpiActivation on is the plain product (0) with a pointwise activation on its sums
+    const int act = epi_code >= kEpiActivation ? epi_code - kEpiActivation + 1 : 0;
+    const int epi = act ? 0 : epi_code;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;        // tiles need 1024-byte alignment
     unsigned char* aligned = smem_raw + (base - smem_addr(smem_raw));
@@ -385,6 +388,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         tmem_ld32(tmem_row + (uint32_t)((c0 + cc) * 32), v);
                         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                         if (epi == 0) {
+                            if (act) {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(activate(__uint_as_float(v[i]), act - 1));
+                            }
                             // 32 columns = four 16-byte pieces, at pieces 4*cc .. 4*cc+3 of the row
 #pragma unroll
                             for (int piece = 0; piece < 4; ++piece) {
@@ -436,6 +443,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int col = n0 + c * 32;
                     if (row >= M || col >= N) continue;
                     if (epi == 0) {
+                        if (act) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(activate(__uint_as_float(v[i]), act - 1));
+                        }
                         store_values<OutT, 32>(C + (size_t)row * ldc + col, v, min(32, N - col), vec_ok);
                     } else {
                         // SwiGLU: the 32 columns are two blocks of 8 gate features followed by
@@ -511,7 +522,8 @@ namespace {
 int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_f32, int M, int N, int K,
         int epilogue, const RopeKV& rope, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (epilogue < 0 || epilogue > 3) return kErrBadArgument;
+    const bool with_activation = epilogue >= kEpiActivation && epilogue < kEpiActivation + kActivations;
+    if ((epilogue < 0 || epilogue > 3) && !with_activation) return kErrBadArgument;
     if (epilogue == 1 && N % 16 != 0) return kErrUnsupported;
     if (epilogue == 3 && (!out_f32 || ldc % 4 || ((uintptr_t)C % 16))) return kErrUnsupported;
     if (K <= 0 || lda < K || ldw < K || ldc < (epilogue == 1 ? N / 2 : N)) return kErrBadArgument;
@@ -578,9 +590,11 @@ int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int ou
 
 // epilogue 0: C[M,N] = A W^T.  epilogue 1: W's rows come in blocks of 8 gate
 // features followed by their 8 up features, and C[M,N/2] = silu(gate) * up.
+// epilogue kEpiActivation + kind: C[M,N] = activation(A W^T), applied to the float sums.
 GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
                                   int out_f32, int M, int N, int K, int epilogue, cudaStream_t stream) {
-    if (epilogue != 0 && epilogue != 1) return kErrBadArgument;
+    if (epilogue != 0 && epilogue != 1 && !(epilogue >= kEpiActivation && epilogue < kEpiActivation + kActivations))
+        return kErrBadArgument;
     return run(A, lda, W, ldw, C, ldc, out_f32, M, N, K, epilogue, RopeKV{}, stream);
 }
 

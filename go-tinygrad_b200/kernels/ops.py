@@ -357,6 +357,7 @@ def add_layernorm(residual: torch.Tensor, pending: Optional[torch.Tensor], weigh
 
 
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+EPILOGUE_ACTIVATION = 16      # a product's epilogue code from here on: the plain product, then activation (code - 16)
 
 
 def activation(x: torch.Tensor, kind: str) -> None:
@@ -517,11 +518,21 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
     the tokens as the N dimension, up to 128 rows), "tcgen05" (TMA + tensor memory)
     or "tiled" (warp-level MMA).  epilogue="swiglu" (bfloat16, not "tiled"): w is laid out by
     `interleave_gate_up` and out[M, N/2] = silu(gate) * up, computed from the
-    float accumulators."""
+    float accumulators.  epilogue="relu2" | "gelu_tanh" | "silu": out[M, N] is that
+    activation of the product, applied to the float sums inside the tensor-core
+    kernels, by the `activation` kernel behind the others."""
     _rows2d(x, "linear: x"); _rows2d(w, "linear: w"); _rows2d(out, "linear: out")
     M, K = x.shape
     N = w.shape[0]
-    _need(epilogue in ("none", "swiglu"), f"linear: unknown epilogue {epilogue!r}")
+    if epilogue in ACTIVATIONS:
+        fused = (x.dtype == torch.bfloat16 and kind != "tiled" and K % 8 == 0 and x.stride(0) % 8 == 0
+                 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+                 and out.data_ptr() % 16 == 0 and out.stride(0) % (4 if out.dtype == torch.float32 else 8) == 0)
+        if not fused:
+            linear(x, w, out, kind=kind)
+            activation(out, epilogue)
+            return
+    _need(epilogue in ("none", "swiglu") or epilogue in ACTIVATIONS, f"linear: unknown epilogue {epilogue!r}")
     n_out = N // 2 if epilogue == "swiglu" else N
     _need(w.shape[1] == K and tuple(out.shape) == (M, n_out),
           f"linear: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} (epilogue {epilogue})")
@@ -554,6 +565,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
         most = WARP_LEVEL_MAX_ROWS if kind == "skinny" else SKINNY_MAX_ROWS
         _need(M <= most, f"linear: the weight-streaming kernel {kind!r} takes at most {most} rows")
     out_f32 = 1 if out.dtype == torch.float32 else 0
+    epi_code = 1 if epilogue == "swiglu" else EPILOGUE_ACTIVATION + ACTIVATIONS[epilogue] if epilogue in ACTIVATIONS else 0
     if kind == "tiled":
         _need(epilogue == "none", "linear: the warp-level kernel has no fused epilogue")
         code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
@@ -564,12 +576,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
         scratch = torch.empty(int(_fn("gtg_gemm_bf16_swapab_scratch_floats")(M, N, K)), dtype=torch.float32,
                               device=x.device)
         code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
-                           out_f32, M, N, K, 1 if epilogue == "swiglu" else 0, _ptr(scratch), _stream())
+                           out_f32, M, N, K, epi_code, _ptr(scratch), _stream())
     else:
         if epilogue == "swiglu":
             _need(N % 16 == 0, f"linear: the fused SwiGLU needs a multiple of 16 rows of w, got {N}")
         code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
-                           out_f32, M, N, K, 1 if epilogue == "swiglu" else 0, _stream())
+                           out_f32, M, N, K, epi_code, _stream())
     _check(code, "linear(bfloat16)")
 
 

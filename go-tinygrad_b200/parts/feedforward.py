@@ -1,7 +1,8 @@
 """Feed-forwards.
 
 ``dense``: down(act(up(x))) without a gate; ``activation`` is "relu2" (the
-square of relu), "gelu_tanh" or "silu", applied in float.  Parameters:
+square of relu), "gelu_tanh" or "silu", applied in float (in bfloat16 to the
+up product's float sums, in its epilogue).  Parameters:
 ``hidden_size``, ``intermediate_size``, ``activation`` and the tensor names
 ``up``, ``down``.  The reference has no ungated feed-forward.
 
@@ -94,8 +95,12 @@ class DenseFeedForward(FeedForward):
         rt = ctx.rt
         n = x.shape[0]
         act = rt.empty(n, (self.inter + 7) // 8 * 8)[:, : self.inter]
-        ops.linear(x, self.w_up, act)
-        ctx.trace("up", lambda: act.clone())
-        ops.activation(act, self.activation)
+        if ctx.op_hook is None:
+            # the activation rides in the product's epilogue, on its float sums, where the kernel has one
+            ops.linear(x, self.w_up, act, epilogue=self.activation)
+        else:
+            ops.linear(x, self.w_up, act)
+            ctx.trace("up", lambda: act.clone())
+            ops.activation(act, self.activation)
         ctx.trace("gate_act", act)
         return emit_update(act, self.w_down, ctx)

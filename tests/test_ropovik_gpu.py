@@ -304,6 +304,29 @@ def test_activations_cap_and_the_projection_beside_a_kept_tensor(dtype):
         block.forward(stream, context(rt, [6], [0], [0]), None)      # nothing was kept in that step
 
 
+@pytest.mark.parametrize("rows", [3, 16, 40, 128, 300])
+def test_activation_in_the_epilogue_of_every_product(rows):
+    """The dense feed-forward's activation applied to the float sums inside the product (one kernel per
+    range of row counts), against the product followed by the activation kernel and against float64."""
+    rng = np.random.default_rng(rows)
+    for K, N in ((64, 72), (256, 1000)):
+        x = t32(rng.standard_normal((rows, K))).to(torch.bfloat16)
+        w = t32(rng.standard_normal((N, K)) * 0.2).to(torch.bfloat16)
+        ref = x.float().cpu().numpy().astype(np.float64) @ w.float().cpu().numpy().astype(np.float64).T
+        for kind, fn in (("relu2", plain.relu_squared), ("silu", plain.silu),
+                         ("gelu_tanh", lambda v: 0.5 * v * (1 + np.tanh(np.sqrt(2 / np.pi) * (v + 0.044715 * v ** 3))))):
+            fused = torch.empty(rows, N, dtype=torch.bfloat16, device=DEV)
+            ops.linear(x, w, fused, epilogue=kind)
+            want = fn(ref)
+            assert np.abs(fused.float().cpu().numpy() - want).max() <= 1e-2 * max(1.0, np.abs(want).max()), (kind, K, N)
+    # float32 and unaligned operands take the product and then the activation kernel: same answer
+    x32, w32 = t32(rng.standard_normal((rows, 20))), t32(rng.standard_normal((9, 20)))
+    out = torch.empty(rows, 9, device=DEV)
+    ops.linear(x32, w32, out, epilogue="relu2")
+    want = plain.relu_squared(x32.cpu().numpy().astype(np.float64) @ w32.cpu().numpy().astype(np.float64).T)
+    assert np.abs(out.cpu().numpy() - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+
+
 def _attention_part(dtype, heads, kv_heads, dim, rot, scale, hidden, wq, wk, wo):
     position = PartSpec("none", {}) if rot is None else PartSpec("rotary", {
         "head_dim": dim, "rotary_dim": rot["dims"], "theta": rot["base"],
