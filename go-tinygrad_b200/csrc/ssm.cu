@@ -168,8 +168,10 @@ __global__ void causal_conv_step_kernel(const T* __restrict__ in, int ld_in, con
 // partial sums of y_t[p] meet by shuffles, four tokens' worth at a time so that
 // their latencies overlap.  Tokens are walked strictly in order: the result does
 // not depend on the cut of the sequence into steps, on the batch or on the slices.
-// x, B and C of kTile tokens at a time are staged in shared memory.
-constexpr int kTile = 16;
+// x, B and C of a tile of tokens at a time are staged in shared memory: kMaxTile for the
+// usual state sizes (up to 256 rows), kPlainTile for the others (up to 512 rows).
+constexpr int kMaxTile = 32;
+constexpr int kPlainTile = 16;
 constexpr int kRowsPerThread = 16;
 
 __device__ __forceinline__ void copy_async_16(void* smem_dst, const void* gmem_src) {
@@ -200,6 +202,7 @@ __global__ void ssm_scan_kernel(const T* __restrict__ x, int ld_x, const float2*
     extern __shared__ __align__(16) float smem[];
     constexpr int kVec = 16 / (int)sizeof(T);
     const int R = RT ? RT : R_, N = RT ? RT * KR : N_;
+    constexpr int kTile = RT ? kMaxTile : kPlainTile;        // tokens staged at a time
     float2* sBC = reinterpret_cast<float2*>(smem);          // two tiles of kTile * N pairs
     float* sx = smem + 4 * kTile * N;                       // kTile * PS
     float2* sda = reinterpret_cast<float2*>(sx + kTile * PS + ((kTile * PS) & 1));   // kTile pairs (dt, a)
@@ -604,6 +607,8 @@ GTG_API int gtg_ssm_scan(int dtype, const void* x, int ld_x, const float* bc, in
     if ((N + R - 1) / R > kRowsPerThread) return kErrUnsupported;
     const int threads = (PS * R + 31) / 32 * 32;
     if (threads > 1024) return kErrUnsupported;
+    const bool constants = aligned && N == R * 16 && (R == 2 || R == 4 || R == 8 || R == 16);   // R and N known to the kernel
+    const int kTile = constants ? kMaxTile : kPlainTile;
     size_t smem = (size_t)(4 * kTile * N + kTile * PS + 1 + 2 * kTile) * sizeof(float);
     if (aligned) smem += (size_t)2 * kTile * PS * (dtype == 0 ? 4 : 2);
     if (smem > 200 * 1024) return kErrUnsupported;
@@ -617,7 +622,7 @@ GTG_API int gtg_ssm_scan(int dtype, const void* x, int ld_x, const float* bc, in
     } while (0)
 #define GTG_SCAN_LAUNCH(T, ASYNC)                                                                                        \
     do {                                                                                                                 \
-        if (ASYNC && N == R * 16) {              /* the usual state sizes: R and N constants of the kernel */            \
+        if (ASYNC && constants) {                /* the usual state sizes: R and N constants of the kernel */            \
             if (R == 2) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 2, 2);                                                          \
             if (R == 4) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 4, 2);                                                          \
             if (R == 8) GTG_SCAN_LAUNCH_KR(T, ASYNC, 16, 8, 2);                                                          \
