@@ -108,6 +108,102 @@ __global__ void causal_conv_silu_bf16_vec_kernel(const bf16* __restrict__ in, in
     *reinterpret_cast<uint4*>(out + (size_t)n * ld_out + c) = o;
 }
 
+// The same for a prompt in bfloat16: a thread takes 8 neighbouring channels through a run
+// of kConvRun tokens, with its taps and the last TAPS-1 inputs in registers, so that
+// every input is loaded once (16 bytes, all of a run's loads in flight together) and the
+// taps once per run.  Where a new sequence
+// begins inside the run the window is read afresh from that sequence's state.  The sum
+// has the order of the kernels above: bias, then the taps oldest first.
+constexpr int kConvRun = 8;
+template <int TAPS>
+__global__ void causal_conv_silu_bf16_run_kernel(const bf16* __restrict__ in, int ld_in, const float* __restrict__ w,
+                                                 const float* __restrict__ bias, const float* __restrict__ conv_state,
+                                                 bf16* __restrict__ out, int ld_out, const int* __restrict__ token_seq,
+                                                 const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                                                 int n_tokens, int C, int n_plain, float* __restrict__ pairs) {
+    chain_release();
+    chain_wait();
+    constexpr int keep = TAPS - 1;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= C) return;
+    const int n0 = blockIdx.x * kConvRun;
+    float wt[TAPS][8], bs[8], win[keep > 0 ? keep : 1][8];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+        const float4* wp = reinterpret_cast<const float4*>(w + (size_t)j * C + c);
+        const float4 a = wp[0], d = wp[1];
+        wt[j][0] = a.x; wt[j][1] = a.y; wt[j][2] = a.z; wt[j][3] = a.w; wt[j][4] = d.x; wt[j][5] = d.y; wt[j][6] = d.z; wt[j][7] = d.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) bs[e] = bias ? bias[c + e] : 0.f;
+    auto widen = [](const uint4& raw, float* v) {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+    };
+    int seq = -1;
+    const int n_end = min(n0 + kConvRun, n_tokens);
+    // all of the run's inputs are asked for before the first is used
+    uint4 raw[kConvRun];
+    int seq_of[kConvRun];
+#pragma unroll
+    for (int t = 0; t < kConvRun; ++t) {
+        const int n = min(n0 + t, n_tokens - 1);
+        raw[t] = *reinterpret_cast<const uint4*>(in + (size_t)n * ld_in + c);
+        seq_of[t] = token_seq[n];
+    }
+#pragma unroll
+    for (int t = 0; t < kConvRun; ++t) {
+        const int n = n0 + t;
+        if (n >= n_end) break;
+        const int b = seq_of[t];
+        if (b != seq) {                                   // the run's first token, or a new sequence: fill the window
+            seq = b;
+            const int i = n - cu_seqlens[b];
+            const float* st = conv_state + (size_t)slots[b] * keep * C;
+#pragma unroll
+            for (int j = 0; j < keep; ++j) {
+                const int back = keep - j;
+                if (i - back >= 0) {
+                    widen(*reinterpret_cast<const uint4*>(in + (size_t)(n - back) * ld_in + c), win[j]);
+                } else {
+                    const float4* sp = reinterpret_cast<const float4*>(st + (size_t)(keep + i - back) * C + c);
+                    const float4 a = sp[0], d = sp[1];
+                    win[j][0] = a.x; win[j][1] = a.y; win[j][2] = a.z; win[j][3] = a.w;
+                    win[j][4] = d.x; win[j][5] = d.y; win[j][6] = d.z; win[j][7] = d.w;
+                }
+            }
+        }
+        float cur[8], acc[8];
+        widen(raw[t], cur);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float a = bs[e];
+#pragma unroll
+            for (int j = 0; j < keep; ++j) a = fmaf(wt[j][e], win[j][e], a);
+            acc[e] = silu_f(fmaf(wt[keep][e], cur[e], a));
+        }
+#pragma unroll
+        for (int j = 0; j + 1 < keep; ++j)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) win[j][e] = win[j + 1][e];
+        if (keep > 0) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) win[keep - 1][e] = cur[e];
+        }
+        if (c >= n_plain) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) pairs[pair_index(n, c + e, n_plain, C)] = acc[e];
+        } else {
+            uint4 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+            *reinterpret_cast<uint4*>(out + (size_t)n * ld_out + c) = o;
+        }
+    }
+}
+
 // After the convolution: the state becomes the last taps-1 inputs of each
 // sequence, the step's rows included.  One thread per (sequence, channel) walks
 // oldest to newest, so a short step shifts the old entries without overtaking itself.
@@ -511,6 +607,14 @@ GTG_API int gtg_causal_conv_silu(int dtype, const void* in, int ld_in, const flo
         ((uintptr_t)out % 16) == 0 && ((uintptr_t)conv_state % 16) == 0 && ((uintptr_t)w % 16) == 0 &&
         n_plain % 8 == 0 && (C - n_plain) % 16 == 0) {
         const int per_block = C / 8 < 128 ? (C / 8 + 31) / 32 * 32 : 128;
+        if (n_tokens >= 4 * kConvRun && taps >= 2 && taps <= 4) {            // a prompt: runs of tokens per thread
+            const dim3 grid_run((n_tokens + kConvRun - 1) / kConvRun, (C / 8 + per_block - 1) / per_block);
+#define GTG_CONV_RUN(TAPS) launch_chained(causal_conv_silu_bf16_run_kernel<TAPS>, grid_run, dim3(per_block), 0, stream, (const bf16*)in, ld_in, w, bias, conv_state, (bf16*)out, ld_out, token_seq, cu_seqlens, slots, n_tokens, C, n_plain, pairs)
+            if (taps == 2) return GTG_CONV_RUN(2);
+            if (taps == 3) return GTG_CONV_RUN(3);
+            return GTG_CONV_RUN(4);
+#undef GTG_CONV_RUN
+        }
         const dim3 grid_vec(n_tokens, (C / 8 + per_block - 1) / per_block);
         return launch_chained(causal_conv_silu_bf16_vec_kernel, grid_vec, dim3(per_block), 0, stream, (const bf16*)in, ld_in, w, bias, conv_state, (bf16*)out, ld_out, token_seq, cu_seqlens, slots, C, taps, n_plain, pairs);
     }

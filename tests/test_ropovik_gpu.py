@@ -172,7 +172,7 @@ def test_rotary_table_under_yarn_scaling():
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_convolution_carries_its_last_inputs_across_portions(dtype):
     rng = np.random.default_rng(1)
-    for C, taps in ((40, 4), (130, 2), (16, 1), (24, 6)):
+    for C, taps in ((40, 4), (130, 2), (16, 1), (24, 6), (48, 4), (64, 3), (32, 2)):
         T = 37
         x = t32(rng.standard_normal((2 * T, C))).to(TORCH[dtype])
         w, b = np.float32(rng.standard_normal((C, taps))), np.float32(rng.standard_normal(C))
@@ -196,6 +196,12 @@ def test_convolution_carries_its_last_inputs_across_portions(dtype):
             at += n
         lim = 1e-5 if dtype == "float32" else 1e-2
         assert np.abs(got.float().cpu().numpy() - want).max() <= lim * max(1.0, np.abs(want).max())
+        # both sequences whole in one step (a prompt-sized step: a thread walks a run of tokens, and the
+        # second sequence begins inside a run)
+        whole = torch.empty(2 * T, C, dtype=TORCH[dtype], device=DEV)
+        ops.causal_conv_silu(x, t32(w.T.copy()), t32(b), torch.zeros(5, max(taps - 1, 0), C, device=DEV), whole,
+                             i32([0] * T + [1] * T), i32([0, T, 2 * T]), i32([3, 0]))
+        assert np.abs(whole.float().cpu().numpy() - want).max() <= lim * max(1.0, np.abs(want).max())
         if C % 4 == 0:                                     # the last half of the channels as float pairs (U_q, V_q)
             q, n_all = C // 4, 2 * T
             plain_out = torch.empty(n_all, C - 2 * q, dtype=TORCH[dtype], device=DEV)
