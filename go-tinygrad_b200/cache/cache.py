@@ -8,7 +8,9 @@ with storage of its own -- its own pages, page pool and block table -- so that
 layers that keep every key and layers that keep a window do not share storage.
 
 Storage of a group: ``pages[entry, page, 0|1, kv_head, token(64), channel]``
-(keys at 0, values at 1).  ``block_table[slot, i]`` is the page holding tokens
+(keys at 0, values at 1; a request with ``planes=1`` has the key plane only and
+its view hands out the key plane as the value plane too: a mixer whose values
+are a part of what it stores as keys).  ``block_table[slot, i]`` is the page holding tokens
 ``[64*i, 64*i+64)`` of the sequence in `slot`.  A sequence holds
 ceil(length/64) pages per group -- a group that keeps a window gives back, as
 the sequence grows, the pages that have slid out of it -- and pages and the
@@ -37,6 +39,7 @@ class KVRequest:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: every key is kept
+    planes: int = 2                   # 2: keys and values; 1: keys only (the values are a part of the key rows)
 
 
 @dataclass(frozen=True)
@@ -82,7 +85,9 @@ class _KVGroup:
                  pages_per_seq: int, dtype: torch.dtype, device: torch.device):
         self.request = request
         self.pool = PagePool(n_pages)
-        self.storage = torch.zeros((n_entries, n_pages, 2, request.n_kv_heads, PAGE_TOKENS,
+        if request.planes not in (1, 2):
+            raise ValueError(f"a key/value store has 1 or 2 planes, not {request.planes}")
+        self.storage = torch.zeros((n_entries, n_pages, request.planes, request.n_kv_heads, PAGE_TOKENS,
                                     request.head_dim), dtype=dtype, device=device)
         self.table_host = torch.zeros((n_slots, pages_per_seq), dtype=torch.int32)
         if device.type == "cuda":
@@ -93,7 +98,7 @@ class _KVGroup:
 
     def view(self, entry: int) -> KVEntryView:
         s = self.storage[entry]
-        return KVEntryView(s[:, 0], s[:, 1], self.table, self.request.n_kv_heads,
+        return KVEntryView(s[:, 0], s[:, self.request.planes - 1], self.table, self.request.n_kv_heads,
                            self.request.head_dim, self.request.window)
 
 

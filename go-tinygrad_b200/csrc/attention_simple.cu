@@ -9,21 +9,27 @@
 // expf, never a fast approximation.  Keys are walked 32 at a time from lo, so
 // the value for a (token, head) depends on nothing but its own keys: not on the
 // batch, not on how the tokens were cut into steps.
+//
+// `vd` is how many channels a value has: the first vd channels of a row of the
+// value plane (vd = hd for ordinary heads).  A mixer whose values are a leading
+// part of what it stores as keys passes the key plane for both and a smaller vd;
+// the output then has vd channels per head.
 #include "common.cuh"
 #include <math.h>
 
 namespace {
 constexpr int kWarps = 4;
-constexpr int kMaxPerLane = 8;   // head_dim <= 256
+constexpr int kMaxHeadDim = 2048;
 
-template <typename T>
+// kMaxPerLane: value channels per lane (vd <= 32 * kMaxPerLane)
+template <typename T, int kMaxPerLane>
 __global__ void __launch_bounds__(kWarps * 32)
 attention_simple_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
                         const T* __restrict__ kc, const T* __restrict__ vc, long long page_stride,
                         const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ token_seq, const int* __restrict__ slots,
                         const int* __restrict__ positions,
-                        int N, int n_heads, int n_kv, int hd, float scale, int window) {
+                        int N, int n_heads, int n_kv, int hd, int vd, float scale, int window) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * kWarps + warp;
@@ -71,7 +77,7 @@ attention_simple_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
 #pragma unroll
             for (int j = 0; j < kMaxPerLane; ++j) {
                 const int d = lane + 32 * j;
-                if (d < hd) acc[j] = fmaf(pj, to_f32<T>(vp[d]), acc[j]);
+                if (d < vd) acc[j] = fmaf(pj, to_f32<T>(vp[d]), acc[j]);
             }
         }
         m = m_new;
@@ -80,7 +86,7 @@ attention_simple_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, i
 #pragma unroll
     for (int j = 0; j < kMaxPerLane; ++j) {
         const int d = lane + 32 * j;
-        if (d < hd) out[(size_t)n * ldo + h * hd + d] = from_f32<T>(acc[j] * inv);
+        if (d < vd) out[(size_t)n * ldo + h * vd + d] = from_f32<T>(acc[j] * inv);
     }
 }
 }  // namespace
@@ -89,23 +95,26 @@ GTG_API int gtg_attention_simple(int dtype, const void* q, int ldq, void* out, i
                                  const void* kc, const void* vc, long long page_stride,
                                  const int* block_table, int table_stride,
                                  const int* token_seq, const int* slots, const int* positions,
-                                 int N, int n_heads, int n_kv, int hd, float scale, int window,
+                                 int N, int n_heads, int n_kv, int hd, int vd, float scale, int window,
                                  cudaStream_t stream) {
     if (N <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || hd <= 0) return kErrBadArgument;
-    if (hd > 32 * kMaxPerLane) return kErrUnsupported;
+    if (vd <= 0 || vd > hd) return kErrBadArgument;
+    if (hd > kMaxHeadDim || vd > 32 * 32) return kErrUnsupported;
     const long long warps = (long long)N * n_heads;
     const long long blocks = (warps + kWarps - 1) / kWarps;
     if (blocks > 0x7fffffffLL) return kErrUnsupported;
     const size_t smem = (size_t)kWarps * hd * sizeof(float);
-    if (dtype == 0)
-        attention_simple_kernel<float><<<(unsigned)blocks, kWarps * 32, smem, stream>>>(
-            (const float*)q, ldq, (float*)out, ldo, (const float*)kc, (const float*)vc, page_stride,
-            block_table, table_stride, token_seq, slots, positions, N, n_heads, n_kv, hd, scale, window);
-    else if (dtype == 1)
-        attention_simple_kernel<bf16><<<(unsigned)blocks, kWarps * 32, smem, stream>>>(
-            (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kc, (const bf16*)vc, page_stride,
-            block_table, table_stride, token_seq, slots, positions, N, n_heads, n_kv, hd, scale, window);
+#define GTG_SIMPLE(T, PER)                                                                                   \
+    attention_simple_kernel<T, PER><<<(unsigned)blocks, kWarps * 32, smem, stream>>>(                            \
+        (const T*)q, ldq, (T*)out, ldo, (const T*)kc, (const T*)vc, page_stride, block_table, table_stride,      \
+        token_seq, slots, positions, N, n_heads, n_kv, hd, vd, scale, window)
+    if (dtype == 0) {
+        if (vd <= 256) GTG_SIMPLE(float, 8); else if (vd <= 512) GTG_SIMPLE(float, 16); else GTG_SIMPLE(float, 32);
+    } else if (dtype == 1) {
+        if (vd <= 256) GTG_SIMPLE(bf16, 8); else if (vd <= 512) GTG_SIMPLE(bf16, 16); else GTG_SIMPLE(bf16, 32);
+    }
+#undef GTG_SIMPLE
     else return kErrBadArgument;
     return launch_status();
 }

@@ -665,3 +665,146 @@ GTG_API int gtg_hidden_concat(int dtype, const float* residual, const void* pend
     if (dtype == 1) return launch_chained(hidden_concat_kernel<bf16>, dim3(N), dim3(threads), 0, stream, residual, (const bf16*)pending, other, (bf16*)out, H);
     return kErrBadArgument;
 }
+
+// ---- the norm of an update, added to the hidden state ---------------------------
+// residual[r,:] += rmsnorm(update[r,:] (+ bias)) * weight, everything in float; the
+// arrangement in which a sublayer's output is normed and the sublayers read the
+// hidden state itself.  `image`, if given, receives the new hidden state rounded
+// to T: what the next sublayer's products read.  U is the update's type (the
+// activation type, or float from a product that kept its sums).
+template <typename U, typename T>
+__global__ void rmsnorm_add_kernel(const U* __restrict__ update, const float* __restrict__ bias,
+                                   const float* __restrict__ weight, float eps, float* __restrict__ residual,
+                                   T* __restrict__ image, int H) {
+    chain_release();
+    chain_wait();
+    extern __shared__ float dyn_smem[];
+    float* row = dyn_smem;
+    float* scratch = dyn_smem + H;
+    const size_t base = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float u = to_f32<U>(update[base + i]);
+        if (bias) u += bias[i];
+        row[i] = u;
+        ss += u * u;
+    }
+    const float total = block_sum(ss, scratch);
+    const float s = 1.0f / sqrtf(total / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float x = residual[base + i] + (weight[i] * row[i]) * s;
+        residual[base + i] = x;
+        if (image) image[base + i] = from_f32<T>(x);
+    }
+}
+
+GTG_API int gtg_rmsnorm_add(int dtype, int update_f32, const void* update, const float* bias, const float* weight,
+                            float eps, float* residual, void* image, int R, int H, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (H <= 0) return kErrBadArgument;
+    int threads = 32;
+    while (threads < 1024 && threads * 4 < H) threads *= 2;
+    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    if (smem > 200 * 1024) return kErrUnsupported;
+    cudaError_t e = cudaSuccess;
+#define GTG_NORM_ADD(U, T)                                                                                       \
+    do {                                                                                                         \
+        if (smem > 48 * 1024)                                                                                    \
+            e = cudaFuncSetAttribute(rmsnorm_add_kernel<U, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return (int)e;                                                                     \
+        return launch_chained(rmsnorm_add_kernel<U, T>, dim3(R), dim3(threads), smem, stream, (const U*)update,  \
+                              bias, weight, eps, residual, (T*)image, H);                                        \
+    } while (0)
+    if (dtype == 0) GTG_NORM_ADD(float, float);
+    if (dtype == 1 && update_f32) GTG_NORM_ADD(float, bf16);
+    if (dtype == 1) GTG_NORM_ADD(bf16, bf16);
+#undef GTG_NORM_ADD
+    return kErrBadArgument;
+}
+
+// out[r,:] = T(x[r,:]): the hidden state rounded to the activation type.
+template <typename T>
+__global__ void round_rows_kernel(const float* __restrict__ x, T* __restrict__ out, size_t total) {
+    chain_release();
+    chain_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<T>(x[i]);
+}
+
+GTG_API int gtg_round_rows(int dtype, const float* x, void* out, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 1023) / 1024 > 4096 ? 4096 : (total + 1023) / 1024);
+    if (dtype == 0) return launch_chained(round_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (float*)out, (size_t)total);
+    if (dtype == 1) return launch_chained(round_rows_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, (bf16*)out, (size_t)total);
+    return kErrBadArgument;
+}
+
+// ---- biases ------------------------------------------------------------------------
+// out[m,i] = silu(gu[m,i] + bg[i]) * (gu[m,I+i] + bu[i]) from a product's float sums.
+template <typename T>
+__global__ void swiglu_bias_kernel(const float* __restrict__ gu, const float* __restrict__ bg,
+                                   const float* __restrict__ bu, T* __restrict__ out, int ldo, int M, int I) {
+    chain_release();
+    chain_wait();
+    const size_t total = (size_t)M * I;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t m = idx / I;
+        const int i = (int)(idx % I);
+        const float g = gu[m * 2 * I + i] + (bg ? bg[i] : 0.f);
+        const float u = gu[m * 2 * I + I + i] + (bu ? bu[i] : 0.f);
+        out[m * ldo + i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+GTG_API int gtg_swiglu_bias(int dtype, const float* gu, const float* bg, const float* bu, void* out, int ldo,
+                            int M, int I, cudaStream_t stream) {
+    if (M <= 0 || I <= 0) return 0;
+    const size_t total = (size_t)M * I;
+    const unsigned blocks = (unsigned)((total + 255) / 256 > 8192 ? 8192 : (total + 255) / 256);
+    if (dtype == 0) return launch_chained(swiglu_bias_kernel<float>, dim3(blocks), dim3(256), 0, stream, gu, bg, bu, (float*)out, ldo, M, I);
+    if (dtype == 1) return launch_chained(swiglu_bias_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, gu, bg, bu, (bf16*)out, ldo, M, I);
+    return kErrBadArgument;
+}
+
+// out[m,n] = T(x[m,n] + b[n]) from a product's float sums.
+template <typename T>
+__global__ void add_bias_kernel(const float* __restrict__ x, const float* __restrict__ b, T* __restrict__ out,
+                                int M, int N) {
+    chain_release();
+    chain_wait();
+    const size_t total = (size_t)M * N;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+        out[idx] = from_f32<T>(x[idx] + b[idx % N]);
+}
+
+GTG_API int gtg_add_bias(int dtype, const float* x, const float* b, void* out, int M, int N, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    const size_t total = (size_t)M * N;
+    const unsigned blocks = (unsigned)((total + 255) / 256 > 8192 ? 8192 : (total + 255) / 256);
+    if (dtype == 0) return launch_chained(add_bias_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, b, (float*)out, M, N);
+    if (dtype == 1) return launch_chained(add_bias_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, b, (bf16*)out, M, N);
+    return kErrBadArgument;
+}
+
+// x[m,n] *= sigmoid(g[m,n]), the product evaluated in float: a gate on a mixer's heads.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, int ldx, const T* __restrict__ g, int ldg, int M, int N) {
+    chain_release();
+    chain_wait();
+    const size_t total = (size_t)M * N;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t m = idx / N;
+        const int n = (int)(idx % N);
+        const float gate = 1.0f / (1.0f + expf(-to_f32<T>(g[m * ldg + n])));
+        x[m * ldx + n] = from_f32<T>(to_f32<T>(x[m * ldx + n]) * gate);
+    }
+}
+
+GTG_API int gtg_sigmoid_gate(int dtype, void* x, int ldx, const void* g, int ldg, int M, int N, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    const size_t total = (size_t)M * N;
+    const unsigned blocks = (unsigned)((total + 255) / 256 > 8192 ? 8192 : (total + 255) / 256);
+    if (dtype == 0) return launch_chained(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, ldx, (const float*)g, ldg, M, N);
+    if (dtype == 1) return launch_chained(sigmoid_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, ldx, (const bf16*)g, ldg, M, N);
+    return kErrBadArgument;
+}

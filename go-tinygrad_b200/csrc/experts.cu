@@ -1,0 +1,239 @@
+// A mixture of experts: routing, the ordering of a step's (token, expert) pairs
+// by expert, products over the ordered rows, and the weighted sum that brings a
+// token's experts together again.  Nothing here talks to the host: a step with
+// experts can be recorded as a graph.
+//
+//   route    z = R x + b in float; the `top` largest z (ties: the lower index)
+//            are the token's experts, their weights softmax over those z alone.
+//   arrange  item i = (token i / top, its (i % top)-th expert).  Items of one
+//            expert get consecutive rows, every expert's stretch padded to whole
+//            tiles of `tile` rows, so that a tile of rows has one expert:
+//            row_item[row] = item or -1, item_row[item] = row, tile_expert[tile]
+//            = expert or -1 past the last tile.  Which of an expert's rows an
+//            item gets is arbitrary; no result depends on it, since every row is
+//            computed by itself.
+//   product  C[row,:] = A[source(row),:] . W[expert(row)]^T, tiles of 64 rows,
+//            one accumulator per output walking k in order.
+//   combine  out[t,:] = sum_k weight[t,k] * Y[item_row[t*top+k],:], k in order.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+// ---- route ----------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, const float* __restrict__ bias,
+                 int* __restrict__ chosen, float* __restrict__ weights, int N, int H, int E, int top) {
+    chain_release();
+    chain_wait();
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 4 + warp;
+    if (n >= N) return;
+    float* z = smem + (size_t)warp * E;
+    const T* xr = x + (size_t)n * ldx;
+    for (int e = 0; e < E; ++e) {
+        const float* r = router + (size_t)e * H;
+        float s = 0.f;
+        for (int i = lane; i < H; i += 32) s = fmaf(to_f32<T>(xr[i]), r[i], s);
+        s = warp_sum(s);
+        if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+    }
+    __syncwarp();
+    if (lane == 0) {
+        float best0 = 0.f, total = 0.f;
+        for (int k = 0; k < top; ++k) {
+            int arg = -1;
+            float best = -INFINITY;
+            for (int e = 0; e < E; ++e) {
+                bool taken = false;
+                for (int j = 0; j < k; ++j) taken |= chosen[(size_t)n * top + j] == e;
+                if (taken) continue;
+                const float v = z[e];
+                if (arg < 0 || v > best) { best = v; arg = e; }
+            }
+            if (k == 0) best0 = best;
+            chosen[(size_t)n * top + k] = arg;
+            const float p = expf(best - best0);
+            weights[(size_t)n * top + k] = p;
+            total += p;
+        }
+        const float inv = 1.0f / total;
+        for (int k = 0; k < top; ++k) weights[(size_t)n * top + k] *= inv;
+    }
+}
+
+// ---- arrange --------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+moe_arrange_kernel(const int* __restrict__ chosen, int n_items, int E, int tile, int n_tiles_cap,
+                   int* __restrict__ row_item, int* __restrict__ item_row, int* __restrict__ tile_expert) {
+    chain_release();
+    chain_wait();
+    extern __shared__ int ism[];
+    int* count = ism;            // [E]
+    int* first = ism + E;        // [E] first row of the expert's stretch
+    int* cursor = ism + 2 * E;   // [E]
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = cursor[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_items; i += blockDim.x) atomicAdd(&count[chosen[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int e = 0; e < E; ++e) {
+            first[e] = t * tile;
+            const int tiles = (count[e] + tile - 1) / tile;
+            for (int j = 0; j < tiles; ++j) tile_expert[t + j] = e;
+            t += tiles;
+        }
+        for (; t < n_tiles_cap; ++t) tile_expert[t] = -1;
+    }
+    for (int r = threadIdx.x; r < n_tiles_cap * tile; r += blockDim.x) row_item[r] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
+        const int e = chosen[i];
+        const int row = first[e] + atomicAdd(&cursor[e], 1);
+        row_item[row] = i;
+        item_row[i] = row;
+    }
+}
+
+// ---- product over arranged rows ---------------------------------------------------
+constexpr int BM = 64, BN = 64, BK = 16, PAD = 4;
+
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(256)
+grouped_simt_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ row_item, int item_div,
+                    const TW* __restrict__ W, int ldw, long long expert_stride, const int* __restrict__ tile_expert,
+                    TC* __restrict__ C, int ldc, int N, int K) {
+    chain_release();
+    chain_wait();
+    const int expert = tile_expert[blockIdx.y];
+    if (expert < 0) return;
+    W += (size_t)expert * expert_stride;
+    __shared__ float As[BK][BM + PAD];
+    __shared__ float Ws[BK][BN + PAD];
+    __shared__ int src[BM];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    if (tid < BM) {
+        const int item = row_item[m0 + tid];
+        // item_div > 0: the row's source is its item's token (item / item_div); 0: the row itself
+        src[tid] = item < 0 ? -1 : item_div > 0 ? item / item_div : m0 + tid;
+    }
+    __syncthreads();
+    const int lrow = tid >> 2, lk = (tid & 3) * 4;
+    const int arow = src[lrow];
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = k0 + lk + j;
+            const int wn = n0 + lrow;
+            As[lk + j][lrow] = (arow >= 0 && k < K) ? to_f32<TA>(A[(size_t)arow * lda + k]) : 0.f;
+            Ws[lk + j][lrow] = (wn < N && k < K) ? to_f32<TW>(W[(size_t)wn * ldw + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (src[ty * 4 + i] < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) C[(size_t)m * ldc + n] = from_f32<TC>(acc[i][j]);
+        }
+    }
+}
+
+// ---- combine ----------------------------------------------------------------------
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, int ldy, const int* __restrict__ item_row,
+                                   const float* __restrict__ weights, T* __restrict__ out, int H, int top) {
+    chain_release();
+    chain_wait();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top; ++k)
+            s = fmaf(weights[(size_t)t * top + k], y[(size_t)item_row[(size_t)t * top + k] * ldy + i], s);
+        out[(size_t)t * H + i] = from_f32<T>(s);
+    }
+}
+}  // namespace
+
+GTG_API int gtg_moe_route(int dtype, const void* x, int ldx, const float* router, const float* bias, int* chosen,
+                          float* weights, int N, int H, int E, int top, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E || H <= 0) return kErrBadArgument;
+    const size_t smem = (size_t)4 * E * sizeof(float);
+    if (smem > 48 * 1024) return kErrUnsupported;
+    const dim3 grid((N + 3) / 4);
+    if (dtype == 0) return launch_chained(moe_route_kernel<float>, grid, dim3(128), smem, stream, (const float*)x, ldx, router, bias, chosen, weights, N, H, E, top);
+    if (dtype == 1) return launch_chained(moe_route_kernel<bf16>, grid, dim3(128), smem, stream, (const bf16*)x, ldx, router, bias, chosen, weights, N, H, E, top);
+    return kErrBadArgument;
+}
+
+// Rows the arranged order may need at most: every expert's stretch rounded up to whole tiles.
+GTG_API int gtg_moe_tiles_cap(int n_items, int E, int tile) {
+    return (n_items + tile - 1) / tile + E;
+}
+
+GTG_API int gtg_moe_arrange(const int* chosen, int n_items, int E, int tile, int n_tiles_cap, int* row_item,
+                            int* item_row, int* tile_expert, cudaStream_t stream) {
+    if (n_items <= 0) return 0;
+    if (E <= 0 || tile <= 0 || n_tiles_cap < gtg_moe_tiles_cap(n_items, E, tile)) return kErrBadArgument;
+    const size_t smem = (size_t)3 * E * sizeof(int);
+    if (smem > 48 * 1024) return kErrUnsupported;
+    return launch_chained(moe_arrange_kernel, dim3(1), dim3(1024), smem, stream, chosen, n_items, E, tile, n_tiles_cap,
+                          row_item, item_row, tile_expert);
+}
+
+// C[row,:] = A[source(row),:] . W[expert of the row's tile]^T over tiles of 64 arranged rows.
+// item_div > 0: source(row) = row_item[row] / item_div (the item's token); 0: the row itself.
+// dtype 0: float operands; 1: bfloat16 operands.  c_f32: float result, else the operands' type.
+GTG_API int gtg_moe_product_simt(int dtype, int c_f32, const void* A, int lda, const int* row_item, int item_div,
+                                 const void* W, int ldw, long long expert_stride, const int* tile_expert,
+                                 int n_tiles_cap, void* C, int ldc, int N, int K, cudaStream_t stream) {
+    if (n_tiles_cap <= 0 || N <= 0) return 0;
+    if (K <= 0 || lda < K || ldw < K || ldc < N) return kErrBadArgument;
+    const dim3 grid((N + BN - 1) / BN, n_tiles_cap);
+    if (grid.y > 65535) return kErrUnsupported;
+    if (dtype == 0 && c_f32)
+        return launch_chained(grouped_simt_kernel<float, float, float>, grid, dim3(256), 0, stream, (const float*)A, lda, row_item,
+                              item_div, (const float*)W, ldw, expert_stride, tile_expert, (float*)C, ldc, N, K);
+    if (dtype == 1 && c_f32)
+        return launch_chained(grouped_simt_kernel<bf16, bf16, float>, grid, dim3(256), 0, stream, (const bf16*)A, lda, row_item,
+                              item_div, (const bf16*)W, ldw, expert_stride, tile_expert, (float*)C, ldc, N, K);
+    if (dtype == 1)
+        return launch_chained(grouped_simt_kernel<bf16, bf16, bf16>, grid, dim3(256), 0, stream, (const bf16*)A, lda, row_item,
+                              item_div, (const bf16*)W, ldw, expert_stride, tile_expert, (bf16*)C, ldc, N, K);
+    return kErrBadArgument;
+}
+
+GTG_API int gtg_moe_combine(int dtype, const float* y, int ldy, const int* item_row, const float* weights, void* out,
+                            int N, int H, int top, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (H <= 0 || top <= 0) return kErrBadArgument;
+    if (dtype == 0) return launch_chained(moe_combine_kernel<float>, dim3(N), dim3(256), 0, stream, y, ldy, item_row, weights, (float*)out, H, top);
+    if (dtype == 1) return launch_chained(moe_combine_kernel<bf16>, dim3(N), dim3(256), 0, stream, y, ldy, item_row, weights, (bf16*)out, H, top);
+    return kErrBadArgument;
+}

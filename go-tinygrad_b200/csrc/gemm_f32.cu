@@ -12,7 +12,13 @@ constexpr int BM = 64, BN = 64, BK = 16, PAD = 4;
 template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, int ldw,
-                 TC* __restrict__ C, int ldc, int M, int N, int K) {
+                 TC* __restrict__ C, int ldc, int M, int N, int K,
+                 long long batch_a = 0, long long batch_w = 0, long long batch_c = 0) {
+    // blockIdx.z walks a batch of products of one shape (the heads of a mixer, say):
+    // operand b starts batch_* elements after operand b-1
+    A += (size_t)blockIdx.z * batch_a;
+    W += (size_t)blockIdx.z * batch_w;
+    C += (size_t)blockIdx.z * batch_c;
     __shared__ float As[BK][BM + PAD];
     __shared__ float Ws[BK][BN + PAD];
     const int tid = threadIdx.x;
@@ -85,5 +91,26 @@ GTG_API int gtg_gemm_bf16_simt(const void* A, int lda, const void* W, int ldw, v
         gemm_simt_kernel<bf16, float><<<grid, 256, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, ldw, (float*)C, ldc, M, N, K);
     else
         gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, ldw, (bf16*)C, ldc, M, N, K);
+    return launch_status();
+}
+
+// A batch of products of one shape, C_b[M,N] = A_b[M,K] . W_b[N,K]^T for b < batch, operand b
+// starting batch_a / batch_w / batch_c elements after operand b-1 (rows keep lda / ldw / ldc):
+// the per-head products of a mixer, whose heads lie side by side in a row.  dtype 0: float;
+// 1: bfloat16 operands and result, float sums.
+GTG_API int gtg_gemm_simt_batched(int dtype, const void* A, int lda, long long batch_a, const void* W, int ldw,
+                                  long long batch_w, void* C, int ldc, long long batch_c, int batch,
+                                  int M, int N, int K, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    if (K <= 0 || lda < K || ldw < K || ldc < N) return kErrBadArgument;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+    if (grid.y > 65535 || grid.z > 65535) return kErrUnsupported;
+    if (dtype == 0)
+        gemm_simt_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)A, lda, (const float*)W, ldw, (float*)C, ldc,
+                                                                 M, N, K, batch_a, batch_w, batch_c);
+    else if (dtype == 1)
+        gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, ldw, (bf16*)C, ldc,
+                                                               M, N, K, batch_a, batch_w, batch_c);
+    else return kErrBadArgument;
     return launch_status();
 }

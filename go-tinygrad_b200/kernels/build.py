@@ -40,6 +40,8 @@ LIBRARIES: Dict[str, str] = {
     "attention_tcgen05": "attention_tcgen05.cu",
     "attention_decode_static": "attention_decode_static.cu",
     "ssm": "ssm.cu",
+    "latent": "latent.cu",
+    "experts": "experts.cu",
 }
 # sources a library's file includes textually (they count for staleness)
 INCLUDED_SOURCES: Dict[str, List[str]] = {"attention_decode_static.cu": ["attention_bf16.cu"]}

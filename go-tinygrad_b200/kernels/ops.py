@@ -55,7 +55,19 @@ _SIGNATURES = {
     "gtg_gemm_bf16_swapab_scratch_floats": ("gemm_bf16_swapab", [_I, _I, _I]),
     "gtg_gemm_bf16_swapab_status": ("gemm_bf16_swapab", []),
     "gtg_attention_simple": ("attention_simple", [_I, _P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
-                                                  _I, _I, _I, _I, _F, _I, _P]),
+                                                  _I, _I, _I, _I, _I, _F, _I, _P]),
+    "gtg_rmsnorm_add": ("elementwise", [_I, _I, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
+    "gtg_round_rows": ("elementwise", [_I, _P, _P, _L, _P]),
+    "gtg_swiglu_bias": ("elementwise", [_I, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "gtg_add_bias": ("elementwise", [_I, _P, _P, _P, _I, _I, _P]),
+    "gtg_sigmoid_gate": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _P]),
+    "gtg_gemm_simt_batched": ("gemm_f32", [_I, _P, _I, _L, _P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _P]),
+    "gtg_latent_prepare": ("latent", [_I, _P, _I, _P, _I, _P, _P, _F, _P, _L, _P, _I, _P, _P, _P, _P, _I,
+                                      _I, _I, _I, _I, _I, _I, _P]),
+    "gtg_moe_route": ("experts", [_I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "gtg_moe_arrange": ("experts", [_P, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "gtg_moe_product_simt": ("experts", [_I, _I, _P, _I, _P, _I, _P, _I, _L, _P, _I, _P, _I, _I, _I, _P]),
+    "gtg_moe_combine": ("experts", [_I, _P, _I, _P, _P, _P, _I, _I, _I, _P]),
     "gtg_attention_bf16_supports": ("attention_bf16", [_I]),
     "gtg_attention_decode_scratch_floats": ("attention_bf16", [_I, _I, _I, _I]),
     "gtg_attention_decode_plan": ("attention_bf16", [_I, _I, _I, _I, _I, _L, _I, _P, _P]),
@@ -390,6 +402,66 @@ def hidden_concat(residual: torch.Tensor, pending: Optional[torch.Tensor], other
            "hidden_concat")
 
 
+def rmsnorm_add(update: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor,
+                image: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> None:
+    """residual += rmsnorm(update (+ bias)) * weight, in float: the norm on a
+    sublayer's output.  `update` is float32 or of the activation dtype; `image`,
+    if given, receives the new residual rounded to the activation dtype."""
+    N, H = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "rmsnorm_add: residual must be contiguous float32")
+    _need(update.is_contiguous() and update.shape == residual.shape, "rmsnorm_add: update must be contiguous [N, H]")
+    for name, t in (("weight", weight), ("bias", bias)):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == H),
+              f"rmsnorm_add: {name} must be float32 [H]")
+    if image is not None:
+        _need(image.is_contiguous() and image.shape == residual.shape, "rmsnorm_add: image must be contiguous [N, H]")
+        dt = _dt(image)
+    else:
+        dt = _dt(update)
+    _need(update.dtype == torch.float32 or _dt(update) == dt, "rmsnorm_add: update must be float32 or of the image's dtype")
+    _check(_fn("gtg_rmsnorm_add")(dt, 1 if update.dtype == torch.float32 else 0, _ptr(update), _ptr(bias), _ptr(weight),
+                                  float(eps), _ptr(residual), _ptr(image), N, H, _stream()), "rmsnorm_add")
+
+
+def round_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (float32) rounded to out's dtype."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape == x.shape,
+          "round_rows: x float32 and out, both contiguous and of one shape")
+    _check(_fn("gtg_round_rows")(_dt(out), _ptr(x), _ptr(out), x.numel(), _stream()), "round_rows")
+
+
+def swiglu_bias(gate_up: torch.Tensor, gate_bias: Optional[torch.Tensor], up_bias: Optional[torch.Tensor],
+                out: torch.Tensor) -> None:
+    """out[m,i] = silu(gate_up[m,i] + gate_bias[i]) * (gate_up[m,I+i] + up_bias[i]) from a
+    product's float32 sums [M, 2I]."""
+    _rows2d(out, "swiglu_bias: out")
+    M, two_i = gate_up.shape
+    I = two_i // 2
+    _need(gate_up.dtype == torch.float32 and gate_up.is_contiguous() and two_i % 2 == 0 and tuple(out.shape) == (M, I),
+          "swiglu_bias: gate_up must be contiguous float32 [M, 2I] and out [M, I]")
+    for name, t in (("gate_bias", gate_bias), ("up_bias", up_bias)):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == I), f"swiglu_bias: {name} must be float32 [I]")
+    _check(_fn("gtg_swiglu_bias")(_dt(out), _ptr(gate_up), _ptr(gate_bias), _ptr(up_bias), _ptr(out), out.stride(0), M, I,
+                                  _stream()), "swiglu_bias")
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x + bias, x a product's float32 sums [M, N], out float32 or the activation dtype."""
+    M, N = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape == x.shape,
+          "add_bias: x float32 and out, both contiguous [M, N]")
+    _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == N, "add_bias: bias must be float32 [N]")
+    _check(_fn("gtg_add_bias")(_dt(out), _ptr(x), _ptr(bias), _ptr(out), M, N, _stream()), "add_bias")
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """x *= sigmoid(gate) in place, evaluated in float."""
+    _rows2d(x, "sigmoid_gate: x"); _rows2d(gate, "sigmoid_gate: gate")
+    _need(x.shape == gate.shape and x.dtype == gate.dtype, "sigmoid_gate: x and gate must agree in shape and dtype")
+    _check(_fn("gtg_sigmoid_gate")(_dt(x), _ptr(x), x.stride(0), _ptr(gate), gate.stride(0), x.shape[0], x.shape[1],
+                                   _stream()), "sigmoid_gate")
+
+
 # ------------------------------------------------------------- recurrent mixers
 def _int32(name: str, *tensors) -> None:
     for t in tensors:
@@ -585,6 +657,23 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
     _check(code, "linear(bfloat16)")
 
 
+def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[m, h, :] = x[m, h, :] . w[h]^T for every head h: x [M, heads, K], w
+    [heads, N, K], out [M, heads, N]; x and out may be views whose heads lie side
+    by side in wider rows (any row and head stride, unit channel stride)."""
+    _need(x.dim() == 3 and w.dim() == 3 and out.dim() == 3 and x.stride(2) == 1 and out.stride(2) == 1 and w.is_contiguous(),
+          "linear_heads: x [M, heads, K], w contiguous [heads, N, K], out [M, heads, N] with unit channel strides")
+    M, heads, K = x.shape
+    N = w.shape[1]
+    _need(tuple(w.shape) == (heads, N, K) and tuple(out.shape) == (M, heads, N),
+          f"linear_heads: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
+    _need(x.dtype == w.dtype == out.dtype, "linear_heads: one dtype for x, w and out")
+    if M == 0:
+        return
+    _check(_fn("gtg_gemm_simt_batched")(_dt(x), _ptr(x), x.stride(0), x.stride(1), _ptr(w), K, N * K, _ptr(out),
+                                        out.stride(0), out.stride(1), heads, M, N, K, _stream()), "linear_heads")
+
+
 def linear_add_residual(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) -> bool:
     """residual[M,N] += bfloat16(x[M,K] . w[N,K]^T): the product of a prompt step
     adds its result to a float32 residual stream in its epilogue (tensor reductions,
@@ -683,18 +772,22 @@ def attention_bf16_supports(head_dim: int) -> bool:
 
 
 def attention_simple(q: torch.Tensor, out: torch.Tensor, kv, token_seq, slots, positions,
-                     n_heads: int, scale: float, window: int = 0) -> None:
+                     n_heads: int, scale: float, window: int = 0, value_dim: Optional[int] = None) -> None:
     """One warp per (token, head): the float32 path's attention, for prompts and
-    decode steps alike."""
+    decode steps alike.  `value_dim`: a value is the first so many channels of a
+    row of the value plane (default: all of them), and a head of `out` is that wide."""
     _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
     N = q.shape[0]
+    vd = kv.head_dim if value_dim is None else int(value_dim)
     _need(kv.k.dtype == q.dtype == out.dtype, "attention: q, out and the cache must share a dtype")
-    _need(kv.head_dim <= 256, f"attention: head_dim {kv.head_dim} exceeds 256")
+    _need(kv.head_dim <= 2048 and 0 < vd <= min(kv.head_dim, 1024),
+          f"attention: head_dim {kv.head_dim} exceeds 2048 or the value width {vd} exceeds 1024 or the head")
+    _need(q.shape[1] >= n_heads * kv.head_dim and out.shape[1] >= n_heads * vd, "attention: q or out is too narrow")
     _check_access("attention_simple", 0, kv, slots, positions, token_seq, n_items=N)
     _check(_fn("gtg_attention_simple")(_dt(q), _ptr(q), q.stride(0), _ptr(out), out.stride(0),
                                        _ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table),
                                        kv.table_stride, _ptr(token_seq), _ptr(slots), _ptr(positions),
-                                       N, n_heads, kv.n_kv_heads, kv.head_dim, float(scale), int(window),
+                                       N, n_heads, kv.n_kv_heads, kv.head_dim, vd, float(scale), int(window),
                                        _stream()), "attention_simple")
 
 
@@ -818,6 +911,111 @@ def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: flo
                                             int(n_splits), _ptr(scratch), int(chunk_pages), int(ring_pages),
                                             _stream()),
            "attention_decode_bf16")
+
+
+# ---------------------------------------------------------- attention through a latent
+def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], cos_sin: torch.Tensor, norm_weight: Optional[torch.Tensor],
+                   eps: float, kv, token_seq, slots, positions, q_full: torch.Tensor, n_heads: int, dim: int,
+                   rot: int, rank: int) -> None:
+    """Per token: with a down projection `dkv` [N, rank + rot], the latent
+    rmsnorm(dkv[:, :rank]) * norm_weight and the rotated dkv[:, rank:] go into the
+    token's cache row [rank + rot] of `kv`; and every head's rotated query part
+    q[:, h, dim:] goes to q_full[:, h, rank:] (q [N, heads * (dim + rot)], q_full
+    [N, heads * (rank + rot)]).  Of a rotated part's channels the first 2 P turn,
+    pairs (2i, 2i+1) by cos_sin [N, P, 2]; the rest pass unchanged."""
+    _rows2d(q, "latent_prepare: q"); _rows2d(q_full, "latent_prepare: q_full")
+    N = q.shape[0]
+    _need(rot % 2 == 0 and rot > 0, "latent_prepare: an even number of rotated channels is needed")
+    _need(q.shape[1] == n_heads * (dim + rot) and tuple(q_full.shape) == (N, n_heads * (rank + rot)) and q.dtype == q_full.dtype,
+          "latent_prepare: q must be [N, heads*(dim+rot)] and q_full [N, heads*(rank+rot)] of one dtype")
+    _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.dim() == 3 and cos_sin.shape[0] == N
+          and cos_sin.shape[2] == 2 and 2 * cos_sin.shape[1] <= rot, "latent_prepare: cos_sin must be float32 [N, pairs <= rot/2, 2]")
+    rdims = 2 * cos_sin.shape[1]
+    _int32("latent_prepare", token_seq, slots, positions)
+    if dkv is not None:
+        _rows2d(dkv, "latent_prepare: dkv")
+        _need(tuple(dkv.shape) == (N, rank + rot) and dkv.dtype == q.dtype, "latent_prepare: dkv must be [N, rank+rot] of q's dtype")
+        _need(kv is not None and kv.k.dtype == q.dtype and kv.n_kv_heads == 1 and kv.head_dim == rank + rot,
+              "latent_prepare: the cache entry must hold one head of rank + rot channels")
+        _need(norm_weight is not None and norm_weight.dtype == torch.float32 and norm_weight.is_contiguous()
+              and norm_weight.numel() == rank, "latent_prepare: norm_weight must be float32 [rank]")
+        _check_access("latent_prepare", 0, kv, slots, positions, token_seq, n_items=N)
+        args = (_ptr(kv.k), kv.page_stride, _ptr(kv.block_table), kv.table_stride)
+    else:
+        args = (None, 0, None, 0)
+    _check(_fn("gtg_latent_prepare")(_dt(q), _ptr(q), q.stride(0), _ptr(dkv), dkv.stride(0) if dkv is not None else 0,
+                                     _ptr(cos_sin), _ptr(norm_weight), float(eps), *args, _ptr(token_seq), _ptr(slots),
+                                     _ptr(positions), _ptr(q_full), q_full.stride(0), N, n_heads, dim, rot, rdims, rank, _stream()),
+           "latent_prepare")
+
+
+# ------------------------------------------------------------------ routed experts
+MOE_TILE_ROWS = 64
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], chosen: torch.Tensor,
+              weights: torch.Tensor) -> None:
+    """Router logits x . router^T + bias in float; chosen[n, :] = the `top` largest
+    (ties: the lower index), weights[n, :] = softmax over those logits alone."""
+    _rows2d(x, "moe_route: x")
+    N, H = x.shape
+    E, top = router.shape[0], chosen.shape[1]
+    _need(router.dtype == torch.float32 and router.is_contiguous() and tuple(router.shape) == (E, H), "moe_route: router must be float32 [E, H]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == E), "moe_route: bias must be float32 [E]")
+    _need(chosen.dtype == torch.int32 and chosen.is_contiguous() and weights.dtype == torch.float32 and weights.is_contiguous()
+          and tuple(chosen.shape) == (N, top) and tuple(weights.shape) == (N, top) and 0 < top <= E,
+          "moe_route: chosen int32 [N, top] and weights float32 [N, top]")
+    _check(_fn("gtg_moe_route")(_dt(x), _ptr(x), x.stride(0), _ptr(router), _ptr(bias), _ptr(chosen), _ptr(weights), N, H, E, top,
+                                _stream()), "moe_route")
+
+
+def moe_tiles_cap(n_items: int, n_experts: int, tile: int = MOE_TILE_ROWS) -> int:
+    """Tiles of `tile` rows that hold any assignment of n_items (token, expert) pairs."""
+    return (n_items + tile - 1) // tile + n_experts
+
+
+def moe_arrange(chosen: torch.Tensor, n_experts: int, row_item: torch.Tensor, item_row: torch.Tensor,
+                tile_expert: torch.Tensor, tile: int = MOE_TILE_ROWS) -> None:
+    """Order the (token, expert) pairs by expert, every expert's rows padded to whole
+    tiles: row_item[row] = pair or -1, item_row[pair] = row, tile_expert[tile] = expert or -1."""
+    n_items = chosen.numel()
+    cap = tile_expert.numel()
+    _int32("moe_arrange", chosen, row_item, item_row, tile_expert)
+    _need(cap >= moe_tiles_cap(n_items, n_experts, tile) and row_item.numel() == cap * tile and item_row.numel() == n_items,
+          "moe_arrange: tile_expert [tiles], row_item [tiles * tile], item_row [pairs]")
+    _check(_fn("gtg_moe_arrange")(_ptr(chosen), n_items, n_experts, tile, cap, _ptr(row_item), _ptr(item_row), _ptr(tile_expert),
+                                  _stream()), "moe_arrange")
+
+
+def moe_product(a: torch.Tensor, row_item: torch.Tensor, item_div: int, w: torch.Tensor, tile_expert: torch.Tensor,
+                out: torch.Tensor) -> None:
+    """out[row, :] = a[source(row), :] . w[expert of the row's tile]^T over arranged
+    rows.  item_div > 0: the source is the pair's token, row_item[row] // item_div
+    (a holds tokens); 0: the row itself (a holds arranged rows).  w [E, N, K]."""
+    _rows2d(a, "moe_product: a"); _rows2d(out, "moe_product: out")
+    E, N, K = w.shape
+    cap = tile_expert.numel()
+    _need(w.is_contiguous() and a.dtype == w.dtype and a.shape[1] == K, "moe_product: a [*, K] and contiguous w [E, N, K] of one dtype")
+    _need(tuple(out.shape) == (cap * MOE_TILE_ROWS, N) and out.dtype in (a.dtype, torch.float32), "moe_product: out must be [tiles * 64, N]")
+    _need(item_div > 0 or a.shape[0] == out.shape[0], "moe_product: a must hold the arranged rows")
+    _int32("moe_product", row_item, tile_expert)
+    _check(_fn("gtg_moe_product_simt")(_dt(a), 1 if out.dtype == torch.float32 else 0, _ptr(a), a.stride(0), _ptr(row_item),
+                                       int(item_div), _ptr(w), K, N * K, _ptr(tile_expert), cap, _ptr(out), out.stride(0), N, K,
+                                       _stream()), "moe_product")
+
+
+def moe_combine(y: torch.Tensor, item_row: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = sum_k weights[t, k] * y[item_row[t * top + k], :] (float sums, k in
+    order; out float32 or bfloat16)."""
+    _rows2d(y, "moe_combine: y")
+    N, top = weights.shape
+    H = y.shape[1]
+    _need(y.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (N, H)
+          and weights.dtype == torch.float32 and weights.is_contiguous() and item_row.numel() == N * top,
+          "moe_combine: y float32 [rows, H], weights float32 [N, top], out [N, H]")
+    _int32("moe_combine", item_row)
+    _check(_fn("gtg_moe_combine")(_dt(out), _ptr(y), y.stride(0), _ptr(item_row), _ptr(weights), _ptr(out), N, H, top, _stream()),
+           "moe_combine")
 
 
 # ------------------------------------------------------------------------ sampling

@@ -5,7 +5,7 @@ from .plan import (LayerSpec, ModelPlan, PartSpec, ScheduleEntry, default_schedu
 from .base import (Block, Embedding, FeedForward, Head, Mixer, Norm, Part, PositionEncoding,
                    ResidualStream, Runtime, StepContext, build_part, register_part,
                    registered_parts, unregister_part, walk)
-from . import attention, block, embedding, feedforward, norm, position, recurrent  # noqa: F401  (registration)
+from . import attention, block, embedding, feedforward, latent, norm, position, recurrent  # noqa: F401  (registration)
 
 __all__ = ["LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "default_schedule",
            "plan_weight_specs", "pre_norm_layer", "walk", "Block", "Embedding", "FeedForward", "Head", "Mixer", "Norm", "Part",

@@ -201,6 +201,9 @@ class StepContext:
     total_kv_len: int = 0       # all sequences' lengths after this step, added up (0: not known)
     shared: Dict[Any, Any] = field(default_factory=dict)   # per-step values parts share (rotary tables)
     update_into: Optional["ResidualStream"] = None   # set by a block around a part's forward: see emit_update
+    # set by a block whose norm takes a sublayer's update in float32: a part whose last step
+    # leaves float sums may then return them unrounded instead of in the compute dtype
+    float_updates: bool = False
     step: int = 0               # which step of the model this is (counted by the model; for `op_hook`)
     layer: int = -1             # the layer that is running (set by the engine before each block)
     op_hook: Optional[Callable[[int, int, str, torch.Tensor], None]] = None
@@ -261,11 +264,15 @@ def walk(part: "Part"):
 class ResidualStream:
     """The hidden state between parts: a float32 `residual` [N, H] and a
     `pending` update in the compute dtype that has not been added yet.  A norm
-    adds the pending update and normalises in one pass."""
+    adds the pending update and normalises in one pass.  `image` is the residual
+    rounded to the compute dtype, or None: whoever changes the residual either
+    writes the image along with it or sets it None; a part that reads the hidden
+    state itself (not a norm of it) reads the image and makes it when it is None."""
 
     def __init__(self, residual: torch.Tensor, pending: Optional[torch.Tensor] = None):
         self.residual = residual
         self.pending = pending
+        self.image: Optional[torch.Tensor] = None
 
 
 def emit_update(x: torch.Tensor, w: torch.Tensor, ctx: "StepContext") -> Optional[torch.Tensor]:
@@ -277,6 +284,7 @@ def emit_update(x: torch.Tensor, w: torch.Tensor, ctx: "StepContext") -> Optiona
     stream = ctx.update_into
     if (stream is not None and stream.pending is None and ctx.rt.dtype == torch.bfloat16
             and ops.linear_add_residual(x, w, stream.residual)):
+        stream.image = None
         return None
     out = ctx.rt.empty(x.shape[0], w.shape[0])
     ops.linear(x, w, out)

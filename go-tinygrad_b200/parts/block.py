@@ -10,6 +10,16 @@ one, or the final one) adds it in float32 while it normalises -- unless the
 part, offered the stream (`emit_update`), has added its update in its last
 product's epilogue already and returns None.
 
+``output_norm``: x += norm1(mixer(x)); x += norm2(feed_forward(x)): the norm
+stands on a sublayer's output and the sublayers read the hidden state itself
+(rounded to the compute dtype for their products).  Same four nested specs as
+``pre_norm``; the feed-forward and its norm may be None.  The norms must be of
+kind ``rmsnorm`` (the one norm whose fused form with the addition exists).  A
+sublayer's update may be float32 or of the compute dtype; norm and addition are
+float32, and the kernel that adds also leaves the rounded hidden state for the
+next sublayer (`ResidualStream.image`).  Nothing is left pending.  The reference
+has no such arrangement.
+
 ``concat_projection``: x <- W [x | kept], a projection of the hidden state side
 by side with a tensor an earlier part has kept for the step under the name
 ``source`` in the step's shared values (the token embedding keeps its output
@@ -64,6 +74,59 @@ class PreNormBlock(Block):
         ctx.trace("hidden_post_ffn", lambda: _hidden(stream))
 
 
+def hidden_image(stream: ResidualStream, ctx: StepContext) -> torch.Tensor:
+    """The hidden state in the compute dtype, for a part that reads it un-normed:
+    the residual itself in float32, else its rounded image (made here if nobody
+    left one).  A pending update is added first."""
+    if stream.pending is not None:
+        stream.residual += stream.pending.float()
+        stream.pending, stream.image = None, None
+    if ctx.rt.dtype == torch.float32:
+        return stream.residual
+    if stream.image is None:
+        stream.image = ctx.rt.empty(*stream.residual.shape)
+        ops.round_rows(stream.residual, stream.image)
+    return stream.image
+
+
+@register_part("block", "output_norm")
+class OutputNormBlock(Block):
+    sub_parts = (("mixer_norm", "norm"), ("mixer", "mixer"),
+                 ("feed_forward_norm", "norm"), ("feed_forward", "feed_forward"))
+    optional_parts = ("feed_forward_norm", "feed_forward")
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and norm.kind != "rmsnorm":
+                raise ValueError(f"the output_norm block adds an rmsnorm of each sublayer's output; got a {norm.kind!r} norm")
+
+    def _add_normed(self, update: torch.Tensor, norm, stream: ResidualStream, ctx: StepContext) -> None:
+        image = None
+        if ctx.rt.dtype != torch.float32:
+            image = ctx.rt.empty(*stream.residual.shape)
+        ops.rmsnorm_add(update, norm.weight, norm.eps, stream.residual, image)
+        stream.image = image
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: CacheHandle) -> None:
+        x = hidden_image(stream, ctx)
+        ctx.trace("hidden_in", lambda: stream.residual.clone())
+        ctx.float_updates = True
+        try:
+            update = self.mixer.forward(x, ctx, cache)
+            ctx.trace("o", update)
+            self._add_normed(update, self.mixer_norm, stream, ctx)
+            if self.feed_forward is not None:
+                x = hidden_image(stream, ctx)
+                ctx.trace("mlp_input", x)
+                update = self.feed_forward.forward(x, ctx)
+                ctx.trace("down", update)
+                self._add_normed(update, self.feed_forward_norm, stream, ctx)
+        finally:
+            ctx.float_updates = False
+        ctx.trace("hidden_post_ffn", lambda: stream.residual.clone())
+
+
 @register_part("block", "concat_projection")
 class ConcatProjection(Block):
     def __init__(self, spec):
@@ -86,5 +149,6 @@ class ConcatProjection(Block):
         both = ctx.rt.empty(stream.residual.shape[0], 2 * self.hidden)
         ops.hidden_concat(stream.residual, stream.pending, kept, both)
         stream.pending = None
+        stream.image = None
         ops.linear(both, self.w, stream.residual)
         ctx.trace("hidden_in", lambda: stream.residual.clone())

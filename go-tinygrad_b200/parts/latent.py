@@ -1,0 +1,134 @@
+"""Attention through a latent.
+
+A token keeps, instead of keys and values per head, one latent vector c of
+``kv_rank`` channels (a down projection of the mixer's input, RMS-normed with a
+weight of its own) and one rotated key part of ``rot_dim`` channels that all
+heads share (further rows of the same down projection, not normed).  Head h has
+a query [a_h | b_h] of ``head_dim`` unrotated and ``rot_dim`` rotated channels,
+an unrotated key U_h c and a value V_h c; its score against an earlier token is
+(a_h . U_h c + b_h' . k') * scale (' = rotated), seen through a causal window.
+The heads, side by side, are multiplied by sigmoid(G x) where the part has a
+gate, and projected by O.  The reference has no such mixer.
+
+What runs: one product gives q, the gate and the down projection; one kernel
+norms the latent, rotates the shared key part, stores both in the token's cache
+row [c | k'] and rotates the b_h; a product per head folds U_h into the query,
+a_h -> U_h^T a_h, so that query rows [U_h^T a_h | b_h'] meet cache rows directly
+(a_h . U_h c = U_h^T a_h . c); attention then runs over one shared key/value
+head of kv_rank + rot_dim channels whose values are its first kv_rank channels;
+a product per head applies V_h to the attended latents.  The cache holds
+kv_rank + rot_dim numbers a token and one plane, whatever the head count.
+
+Parameters: ``hidden_size``, ``n_heads``, ``head_dim``, ``rot_dim``, ``v_dim``,
+``kv_rank``, ``window`` (None: all keys), ``scale`` (None: (head_dim +
+rot_dim)^-1/2), ``eps`` (of the latent's norm), ``position`` (a rotary
+PartSpec over the rotated part: interleaved pairs; it may rotate fewer
+channels than rot_dim), ``own_kv`` (False: no down projection, the run reads
+another run's cache rows), and the tensor names ``q``, ``dkv``, ``dkv_norm``,
+``uk``, ``uv``, ``gate`` (None: no gate), ``o``.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Mapping, Optional
+
+import torch
+
+from ..cache import CacheHandle, KVRequest, Request
+from ..kernels import ops
+from ..weights.binder import WeightSpec
+from .base import Mixer, Runtime, StepContext, build_part, emit_update, register_part
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.param("hidden_size"))
+        self.n_heads = int(self.param("n_heads"))
+        self.dim = int(self.param("head_dim"))
+        self.rot = int(self.param("rot_dim"))
+        self.v_dim = int(self.param("v_dim"))
+        self.rank = int(self.param("kv_rank"))
+        window = self.p.get("window")
+        self.window = int(window) if window else None
+        scale = self.p.get("scale")
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.dim + self.rot)
+        self.eps = float(self.param("eps"))
+        self.own_kv = bool(self.p.get("own_kv", True))
+        self.position = build_part("position", self.param("position"))
+        if self.position.pairing != "interleaved" or (self.position.rotary_dim or self.rot) > self.rot:
+            raise ValueError("latent attention rotates interleaved pairs within its rotated part")
+        if self.rot % 2:
+            raise ValueError(f"the rotated part needs an even number of channels, got {self.rot}")
+        wanted = ["q", "uk", "uv", "o"] + (["dkv", "dkv_norm"] if self.own_kv else [])
+        self.names = {k: str(self.param(k)) for k in wanted}
+        gate = self.p.get("gate")
+        if gate:
+            self.names["gate"] = str(gate)
+        self.row = self.rank + self.rot                     # a cache row, and a folded query row of a head
+        self.q_dim = self.n_heads * (self.dim + self.rot)
+        self.g_dim = self.n_heads * self.v_dim if gate else 0
+        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.norm_w = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        H = self.n_heads
+        specs = [WeightSpec(self.names["q"], (self.q_dim, self.hidden))]
+        if self.own_kv:
+            specs += [WeightSpec(self.names["dkv"], (self.row, self.hidden)),
+                      WeightSpec(self.names["dkv_norm"], (self.rank,), role="vector", mean=1.0)]
+        specs += [WeightSpec(self.names["uk"], (H * self.dim, self.rank)),
+                  WeightSpec(self.names["uv"], (H * self.v_dim, self.rank))]
+        if "gate" in self.names:
+            specs.append(WeightSpec(self.names["gate"], (H * self.v_dim, self.hidden)))
+        specs.append(WeightSpec(self.names["o"], (self.hidden, H * self.v_dim)))
+        return specs
+
+    def children(self):
+        return [self.position]
+
+    def cache_requests(self) -> List[Request]:
+        return [KVRequest(1, self.row, self.window, planes=1)] if self.own_kv else []
+
+    def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        H = self.n_heads
+        parts = [tensors[self.names["q"]]]
+        if "gate" in self.names:
+            parts.append(tensors[self.names["gate"]])
+        if self.own_kv:
+            parts.append(tensors[self.names["dkv"]])
+            self.norm_w = rt.vector(tensors[self.names["dkv_norm"]])
+        self.w_in = rt.matrix(torch.cat([p.to(rt.dtype) for p in parts], dim=0))
+        # U_h^T per head, [H, rank, dim]: the product that folds U_h into the query reads it as its weight
+        self.w_uk_t = rt.matrix(tensors[self.names["uk"]].to(rt.dtype).reshape(H, self.dim, self.rank).transpose(1, 2))
+        self.w_uv = rt.matrix(tensors[self.names["uv"]]).view(H, self.v_dim, self.rank)
+        self.w_o = rt.matrix(tensors[self.names["o"]])
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheHandle) -> torch.Tensor:
+        rt = ctx.rt
+        kv = cache.kv
+        if kv is None or kv.n_kv_heads != 1 or kv.head_dim != self.row:
+            raise ValueError("latent attention was given a cache entry that does not hold its rows")
+        n, H = x.shape[0], self.n_heads
+        width = self.w_in.shape[0]
+        proj = rt.empty(n, (width + 7) // 8 * 8)[:, :width]
+        ops.linear(x, self.w_in, proj)
+        q = proj[:, : self.q_dim]
+        gate = proj[:, self.q_dim: self.q_dim + self.g_dim] if self.g_dim else None
+        dkv = proj[:, self.q_dim + self.g_dim:] if (self.own_kv and cache.writes) else None
+        rotation = self.position.rotation(ctx)
+        folded = rt.empty(n, H * self.row)
+        ops.latent_prepare(q, dkv, rotation, self.norm_w, self.eps, kv, ctx.token_seq, ctx.slots, ctx.positions,
+                           folded, H, self.dim, self.rot, self.rank)
+        ops.linear_heads(q.view(n, H, self.dim + self.rot)[:, :, : self.dim], self.w_uk_t,
+                         folded.view(n, H, self.row)[:, :, : self.rank])
+        ctx.trace("q_attn", folded)
+        attended = rt.empty(n, H * self.rank)
+        ops.attention_simple(folded, attended, kv, ctx.token_seq, ctx.slots, ctx.positions, H, self.scale,
+                             self.window or 0, value_dim=self.rank)
+        heads = rt.empty(n, (H * self.v_dim + 7) // 8 * 8)[:, : H * self.v_dim]
+        ops.linear_heads(attended.view(n, H, self.rank), self.w_uv, heads.view(n, H, self.v_dim))
+        if gate is not None:
+            ops.sigmoid_gate(heads, gate)
+        ctx.trace("attn", heads)
+        return emit_update(heads, self.w_o, ctx)

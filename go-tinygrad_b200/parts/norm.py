@@ -41,6 +41,8 @@ class RMSNorm(Norm):
         out = ctx.rt.empty(n_out, self.size)
         ops.add_rmsnorm(stream.residual, stream.pending, self.weight, self.eps, out, rows)
         if rows is None:
+            if stream.pending is not None:
+                stream.image = None
             stream.pending = None
         return out
 
@@ -73,5 +75,7 @@ class LayerNorm(Norm):
         out = ctx.rt.empty(n_out, self.size)
         ops.add_layernorm(stream.residual, stream.pending, self.weight, self.bias, self.eps, out, rows)
         if rows is None:
+            if stream.pending is not None:
+                stream.image = None
             stream.pending = None
         return out
