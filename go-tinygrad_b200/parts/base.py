@@ -214,7 +214,8 @@ class StepContext:
         that builds the value, called only when a hook listens.  The names follow
         the reference's per-op hook (model/debug_hooks.go:5-7 and its call sites in
         model/llama.go:1089-1427): hidden_in, normed, q, k, v, q_attn, attn, o,
-        mlp_input, gate_pre, up, gate_act, down, hidden_post_ffn.  A part reports
+        mlp_input, gate_pre, up, gate_act, down, hidden_post_ffn; a routed feed-forward
+        adds "experts", the experts each token uses.  A part reports
         what it materialises: a fused kernel that never writes a value to memory
         has nothing to report under that name."""
         if self.op_hook is not None:

@@ -162,6 +162,7 @@ class RoutedExperts(FeedForward):
         chosen = rt.empty(n, top, dtype=torch.int32)
         weights = rt.empty(n, top, dtype=torch.float32)
         ops.moe_route(x, self.router, self.router_bias, chosen, weights)
+        ctx.trace("experts", chosen)
         tiles = ops.moe_tiles_cap(n * top, E)
         rows = tiles * ops.MOE_TILE_ROWS
         row_item = rt.empty(rows, dtype=torch.int32)

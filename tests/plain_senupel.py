@@ -140,10 +140,18 @@ def route(h, router, router_b, top):
     return chosen, e / e.sum(axis=-1, keepdims=True)
 
 
-def expert_mixture(h, experts, router, router_b, top):
-    """experts: list of (gate, up, down)."""
+def expert_mixture(h, experts, router, router_b, top, chosen=None):
+    """experts: list of (gate, up, down).  `chosen` [T, top], if given, replaces the
+    router's choice (the weights are still the softmax over the chosen logits): a
+    test follows an implementation's choices where two logits were too close to call."""
     h = np.asarray(h, F64)
-    chosen, weights = route(h, router, router_b, top)
+    if chosen is None:
+        chosen, weights = route(h, router, router_b, top)
+    else:
+        z = h @ np.asarray(router, F64).T + np.asarray(router_b, F64)
+        zc = np.take_along_axis(z, np.asarray(chosen), axis=-1)
+        e = np.exp(zc - zc.max(axis=-1, keepdims=True))
+        weights = e / e.sum(axis=-1, keepdims=True)
     out = np.zeros((h.shape[0], np.asarray(experts[0][2]).shape[0]), F64)
     for t in range(h.shape[0]):
         for e, p in zip(chosen[t], weights[t]):
@@ -155,9 +163,10 @@ def expert_mixture(h, experts, router, router_b, top):
 # --------------------------------------------------------------------------
 # the model
 # --------------------------------------------------------------------------
-def forward(config, weights, tokens, keep_layers=False):
+def forward(config, weights, tokens, keep_layers=False, routing=None):
     """Logits [T, vocab] of one whole sequence (and, if asked, the hidden state
-    after every layer [L, T, width])."""
+    after every layer [L, T, width]).  `routing`: {layer: chosen [T, top]} to use
+    instead of the routers' own choices."""
     eps = float(config["norm"]["eps"])
     tokens = np.asarray(tokens)
     T = tokens.shape[0]
@@ -186,9 +195,18 @@ def forward(config, weights, tokens, keep_layers=False):
             else:
                 n, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
                 experts = [tuple(weights[f"{p}mlp.e{e}.{k}"] for k in ("gate", "up", "down")) for e in range(n)]
-                y = expert_mixture(x, experts, weights[p + "mlp.router"], weights[p + "mlp.router.b"], top)
+                y = expert_mixture(x, experts, weights[p + "mlp.router"], weights[p + "mlp.router.b"], top,
+                                   None if routing is None else routing.get(i))
             x = x + rms_norm(y, weights[p + "norm2"], eps)
         if keep_layers:
             after.append(x.copy())
     logits = rms_norm(x, weights["final.norm"], eps) @ np.asarray(weights["head"], F64).T
     return (logits, np.stack(after)) if keep_layers else logits
+
+
+def greedy(config, weights, prompt, n_new):
+    """n_new tokens, each the first maximum of the logits after everything before it."""
+    seq = list(prompt)
+    for _ in range(n_new):
+        seq.append(int(np.argmax(forward(config, weights, seq)[-1])))
+    return seq[len(prompt):]
