@@ -18,7 +18,7 @@
 //     (the head of the row is written by the product with U_h^T).
 // Rotation: of the part's first `rdims` channels, (2i, 2i+1) turn by the angle of pair i, whose cosine and
 // sine (amplitude included) come from the step's table [token, rot/2].
-#include "common.cuh"
+#include "mma_helpers.cuh"
 #include <math.h>
 
 namespace {
@@ -95,4 +95,255 @@ GTG_API int gtg_latent_prepare(int dtype, const void* q, int ldq, const void* dk
                               block_table, table_stride, token_seq, slots, positions, (bf16*)q_full, ldf, n_heads,
                               dim, rot, rdims, rank);
     return kErrBadArgument;
+}
+
+// ---- attention over the latent rows, on the warp-level tensor cores ------------------
+// All heads of a token meet the same cache rows, so the (token, head) pairs of a
+// sequence's new tokens are one list of query rows; a thread block takes 32
+// consecutive ones (two tokens of 16 heads, a quarter of a token of 128, eleven
+// of 3) and walks the pages their windows span, each page staged once in shared
+// memory by cp.async, two pages in flight.  Per page, eight warps as 2 row
+// groups x 4: first every warp multiplies its 16 query rows with a quarter of
+// the page's 64 keys over all rank + rot channels (S, float), the row maxima and
+// sums meet through shared memory (streaming softmax in float, expf), the
+// weights go to shared memory as bfloat16; then every warp adds, for its 16
+// rows, a quarter of the value channels: O[16, rank/4] += P[16, 64] . page[64,
+// quarter], the page's first rank columns read transposed (ldmatrix.trans).  O
+// stays in registers (up to 64 floats a thread at rank 512).  Prompts, portions
+// and single tokens are one code path; a row sees keys lo..pos of its sequence,
+// lo = 0 or pos - window + 1.  Needs rank + rot a multiple of 16 and rank of 8.
+
+namespace {
+constexpr int kTileRows = 32;
+constexpr int kLatThreads = 256;
+constexpr int kPad = 8;              // bfloat16 of padding per staged row: rows fall into different banks
+
+template <int NT>                    // value n-tiles (8 channels) per warp at most: rank <= 32 * NT
+__global__ void __launch_bounds__(kLatThreads)
+latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
+                            const bf16* __restrict__ kc, long long page_stride, const int* __restrict__ block_table,
+                            int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                            const int* __restrict__ start_pos, int n_heads, int D, int rank, float scale, int window) {
+    chain_release();
+    chain_wait();
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int b = blockIdx.y;
+    const int tok0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - tok0;
+    const int r0 = blockIdx.x * kTileRows;
+    if (r0 >= n_new * n_heads) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rg = warp & 1, quarter = warp >> 1;
+    const int g = lane >> 2, t = lane & 3;
+    const int ldr = D + kPad;                                   // staged row, in elements
+    bf16* q_s = reinterpret_cast<bf16*>(smem);                  // [32][ldr]
+    bf16* page_s = q_s + kTileRows * ldr;                       // [2][64][ldr]
+    bf16* p_s = page_s + 2 * kPageTokens * ldr;                 // [32][64 + kPad]
+    float* part = reinterpret_cast<float*>(p_s + kTileRows * (kPageTokens + kPad));   // [2][4][32]: maxima, sums
+    int* row_pos = reinterpret_cast<int*>(part + 2 * 4 * kTileRows);                  // [32] position or -1
+    const int start = start_pos[b];
+    const int* table = block_table + (size_t)slots[b] * table_stride;
+    if (tid < kTileRows) {
+        const int r = r0 + tid;
+        row_pos[tid] = r < n_new * n_heads ? start + r / n_heads : -1;
+    }
+    const int chunks = D / 8;
+    for (int id = tid; id < kTileRows * chunks; id += kLatThreads) {
+        const int r = id / chunks, c = id % chunks;
+        const int row = r0 + r;
+        const bool ok = row < n_new * n_heads;
+        const bf16* src = ok ? q + (size_t)(tok0 + row / n_heads) * ldq + (size_t)(row % n_heads) * D + c * 8 : q;
+        cp_async16(smem_u32(q_s + r * ldr + c * 8), src, ok ? 16 : 0);
+    }
+    const int last_row = min(r0 + kTileRows, n_new * n_heads) - 1;
+    const int pos_min = start + r0 / n_heads, pos_max = start + last_row / n_heads;
+    const int lo_min = (window > 0 && pos_min - window + 1 > 0) ? pos_min - window + 1 : 0;
+    const int page_lo = lo_min / kPageTokens, page_hi = pos_max / kPageTokens;
+
+    auto load_page = [&](int buf, int p) {
+        const bf16* src = kc + (size_t)table[p] * page_stride;
+        bf16* dst = page_s + (size_t)buf * kPageTokens * ldr;
+        for (int id = tid; id < kPageTokens * chunks; id += kLatThreads) {
+            const int r = id / chunks, c = id % chunks;
+            cp_async16(smem_u32(dst + r * ldr + c * 8), src + (size_t)r * D + c * 8, 16);
+        }
+    };
+    load_page(0, page_lo);
+    cp_async_commit();
+
+    const int tiles_total = rank / 8;
+    const int per = (tiles_total + 3) / 4;
+    const int tile_lo = quarter * per;
+    const int my_tiles = max(0, min(per, tiles_total - tile_lo));
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    __syncthreads();                                            // row_pos
+    int pos_r[2], lo_r[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        pos_r[hh] = row_pos[rg * 16 + g + hh * 8];
+        lo_r[hh] = (window > 0 && pos_r[hh] - window + 1 > 0) ? pos_r[hh] - window + 1 : 0;
+    }
+
+    for (int p = page_lo; p <= page_hi; ++p) {
+        const int buf = (p - page_lo) & 1;
+        if (p > page_lo) __syncthreads();                       // everyone is done with the page before and its weights
+        if (p + 1 <= page_hi) load_page(buf ^ 1, p + 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();                                        // page p (and q) staged
+        const bf16* pg = page_s + (size_t)buf * kPageTokens * ldr;
+        // S: rows rg*16.., keys quarter*16.. of the page
+        float s[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+        {
+            const uint32_t a_addr = smem_u32(q_s + (rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldr + (lane >> 4) * 8);
+            const uint32_t b_addr = smem_u32(pg + (quarter * 16 + (lane & 7) + (lane >> 4) * 8) * ldr + ((lane >> 3) & 1) * 8);
+            for (int ks = 0; ks < D / 16; ++ks) {
+                uint32_t a[4], b0, b1, b2, b3;
+                ldmatrix_x4(a[0], a[1], a[2], a[3], a_addr + ks * 32);
+                ldmatrix_x4(b0, b1, b2, b3, b_addr + ks * 32);
+                mma_bf16_16816(s[0], a, b0, b1);
+                mma_bf16_16816(s[1], a, b2, b3);
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int hh = e >> 1;
+                const int key = p * kPageTokens + quarter * 16 + j * 8 + t * 2 + (e & 1);
+                const bool seen = pos_r[hh] >= 0 && key <= pos_r[hh] && key >= lo_r[hh];
+                s[j][e] = seen ? s[j][e] * scale : -INFINITY;
+                mx[hh] = fmaxf(mx[hh], s[j][e]);
+            }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
+            if (t == 0) part[quarter * kTileRows + rg * 16 + g + hh * 8] = mx[hh];
+        }
+        __syncthreads();
+        float corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int r = rg * 16 + g + hh * 8;
+            float m_new = m_run[hh];
+#pragma unroll
+            for (int qq = 0; qq < 4; ++qq) m_new = fmaxf(m_new, part[qq * kTileRows + r]);
+            corr[hh] = m_new == -INFINITY ? 1.f : expf(m_run[hh] - m_new);
+            m_run[hh] = m_new;
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const float p0 = s[j][hh * 2] == -INFINITY ? 0.f : expf(s[j][hh * 2] - m_run[hh]);
+                const float p1 = s[j][hh * 2 + 1] == -INFINITY ? 0.f : expf(s[j][hh * 2 + 1] - m_run[hh]);
+                const __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+                // the sum runs over the rounded weights, the ones the values are multiplied with
+                sum[hh] += __bfloat162float(pr.x) + __bfloat162float(pr.y);
+                *reinterpret_cast<__nv_bfloat162*>(p_s + (rg * 16 + g + hh * 8) * (kPageTokens + kPad) + quarter * 16 + j * 8 + t * 2) = pr;
+            }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            sum[hh] += __shfl_xor_sync(0xffffffffu, sum[hh], 1);
+            sum[hh] += __shfl_xor_sync(0xffffffffu, sum[hh], 2);
+            if (t == 0) part[4 * kTileRows + quarter * kTileRows + rg * 16 + g + hh * 8] = sum[hh];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int r = rg * 16 + g + hh * 8;
+            float total = 0.f;
+#pragma unroll
+            for (int qq = 0; qq < 4; ++qq) total += part[4 * kTileRows + qq * kTileRows + r];
+            l_run[hh] = l_run[hh] * corr[hh] + total;
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
+        }
+        // O += P . page[:, my value channels]
+        {
+            const uint32_t a_addr = smem_u32(p_s + (rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * (kPageTokens + kPad) + (lane >> 4) * 8);
+            const uint32_t v_addr = smem_u32(pg + ((lane & 7) + ((lane >> 3) & 1) * 8) * ldr + tile_lo * 8 + (lane >> 4) * 8);
+#pragma unroll
+            for (int ks = 0; ks < kPageTokens / 16; ++ks) {
+                uint32_t a[4];
+                ldmatrix_x4(a[0], a[1], a[2], a[3], a_addr + ks * 32);
+#pragma unroll
+                for (int j = 0; j < NT; j += 2) {
+                    if (j < my_tiles) {
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4_trans(b0, b1, b2, b3, v_addr + (ks * 16 * ldr + j * 8) * 2);
+                        mma_bf16_16816(o[j], a, b0, b1);
+                        if (j + 1 < NT) mma_bf16_16816(o[j + 1], a, b2, b3);
+                    }
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int row = r0 + rg * 16 + g + hh * 8;
+        if (pos_r[hh] < 0 || l_run[hh] <= 0.f) continue;
+        const float inv = 1.0f / l_run[hh];
+        bf16* dst = out + (size_t)(tok0 + row / n_heads) * ldo + (size_t)(row % n_heads) * rank + tile_lo * 8 + t * 2;
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+            if (j < my_tiles)
+                *reinterpret_cast<__nv_bfloat162*>(dst + j * 8) = __floats2bfloat162_rn(o[j][hh * 2] * inv, o[j][hh * 2 + 1] * inv);
+    }
+}
+
+size_t latent_attention_smem(int D) {
+    const size_t ldr = D + kPad;
+    return (kTileRows + 2 * kPageTokens) * ldr * 2 + kTileRows * (kPageTokens + kPad) * 2 + 2 * 4 * kTileRows * 4 + kTileRows * 4;
+}
+}  // namespace
+
+// Whether the tensor-core kernel takes rows of D = rank + rot channels with `rank` value channels.
+GTG_API int gtg_latent_attention_supports(int D, int rank) {
+    return D > 0 && D % 16 == 0 && rank > 0 && rank % 8 == 0 && rank <= 512 && rank <= D && latent_attention_smem(D) <= 220 * 1024;
+}
+
+GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo, const void* kc, long long page_stride,
+                                      const int* block_table, int table_stride, const int* cu_seqlens, const int* slots,
+                                      const int* start_pos, int n_seqs, int max_q_len, int n_heads, int D, int rank,
+                                      float scale, int window, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_q_len <= 0) return 0;
+    if (n_heads <= 0) return kErrBadArgument;
+    if (!gtg_latent_attention_supports(D, rank)) return kErrUnsupported;
+    if (ldq % 8 || ((uintptr_t)q % 16) || ((uintptr_t)kc % 16) || page_stride % 8 || ldo % 2 || ((uintptr_t)out % 4)) return kErrUnsupported;
+    const size_t smem = latent_attention_smem(D);
+    const long long tiles = ((long long)max_q_len * n_heads + kTileRows - 1) / kTileRows;
+    if (tiles > 0x7fffffffLL || n_seqs > 65535) return kErrUnsupported;
+    const dim3 grid((unsigned)tiles, n_seqs);
+#define GTG_LATENT(NT)                                                                                              \
+    do {                                                                                                            \
+        static bool configured = false;                                                                             \
+        if (!configured) {                                                                                          \
+            const cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<NT>,                             \
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);    \
+            if (e != cudaSuccess) return (int)e;                                                                    \
+            configured = true;                                                                                      \
+        }                                                                                                           \
+        return launch_chained(latent_attention_mma_kernel<NT>, grid, dim3(kLatThreads), smem, stream, (const bf16*)q, ldq, \
+                              (bf16*)out, ldo, (const bf16*)kc, page_stride, block_table, table_stride, cu_seqlens, slots, \
+                              start_pos, n_heads, D, rank, scale, window);                                          \
+    } while (0)
+    const int per = ((rank / 8) + 3) / 4;
+    if (per <= 4) GTG_LATENT(4);
+    if (per <= 8) GTG_LATENT(8);
+    GTG_LATENT(16);
+#undef GTG_LATENT
 }

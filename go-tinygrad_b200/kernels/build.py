@@ -42,6 +42,7 @@ LIBRARIES: Dict[str, str] = {
     "ssm": "ssm.cu",
     "latent": "latent.cu",
     "experts": "experts.cu",
+    "gemm_bf16_grouped": "gemm_bf16_grouped.cu",
 }
 # sources a library's file includes textually (they count for staleness)
 INCLUDED_SOURCES: Dict[str, List[str]] = {"attention_decode_static.cu": ["attention_bf16.cu"]}

@@ -62,8 +62,12 @@ _SIGNATURES = {
     "gtg_add_bias": ("elementwise", [_I, _P, _P, _P, _I, _I, _P]),
     "gtg_sigmoid_gate": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _P]),
     "gtg_gemm_simt_batched": ("gemm_f32", [_I, _P, _I, _L, _P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _P]),
+    "gtg_gemm_bf16_grouped": ("gemm_bf16_grouped", [_P, _I, _L, _P, _I, _P, _I, _L, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I,
+                                                    _I, _P, _I, _L, _P]),
     "gtg_latent_prepare": ("latent", [_I, _P, _I, _P, _I, _P, _P, _F, _P, _L, _P, _I, _P, _P, _P, _P, _I,
                                       _I, _I, _I, _I, _I, _I, _P]),
+    "gtg_latent_attention_supports": ("latent", [_I, _I]),
+    "gtg_latent_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
     "gtg_moe_route": ("experts", [_I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "gtg_moe_arrange": ("experts", [_P, _I, _I, _I, _I, _P, _P, _P, _P]),
     "gtg_moe_product_simt": ("experts", [_I, _I, _P, _I, _P, _I, _P, _I, _L, _P, _I, _P, _I, _I, _I, _P]),
@@ -657,10 +661,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
     _check(code, "linear(bfloat16)")
 
 
-def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+def _grouped_ok(a: torch.Tensor, w: torch.Tensor, K: int, *strides: int) -> bool:
+    """Whether the warp-level tensor-core product can address these bfloat16 operands."""
+    return (a.dtype == torch.bfloat16 and K % 8 == 0 and all(s % 8 == 0 for s in strides)
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
     """out[m, h, :] = x[m, h, :] . w[h]^T for every head h: x [M, heads, K], w
     [heads, N, K], out [M, heads, N]; x and out may be views whose heads lie side
-    by side in wider rows (any row and head stride, unit channel stride)."""
+    by side in wider rows (any row and head stride, unit channel stride).  With
+    `gate` (laid out like out) the result is multiplied by sigmoid(gate), in
+    float: in the product's epilogue on the tensor-core route, by a kernel of
+    its own behind the plain product."""
     _need(x.dim() == 3 and w.dim() == 3 and out.dim() == 3 and x.stride(2) == 1 and out.stride(2) == 1 and w.is_contiguous(),
           "linear_heads: x [M, heads, K], w contiguous [heads, N, K], out [M, heads, N] with unit channel strides")
     M, heads, K = x.shape
@@ -668,10 +681,21 @@ def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _need(tuple(w.shape) == (heads, N, K) and tuple(out.shape) == (M, heads, N),
           f"linear_heads: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
     _need(x.dtype == w.dtype == out.dtype, "linear_heads: one dtype for x, w and out")
+    if gate is not None:
+        _need(gate.shape == out.shape and gate.dtype == out.dtype and gate.stride(2) == 1, "linear_heads: gate must be laid out like out")
     if M == 0:
+        return
+    if _grouped_ok(x, w, K, x.stride(0), x.stride(1)):
+        g = (_ptr(gate), gate.stride(0), gate.stride(1)) if gate is not None else (None, 0, 0)
+        _check(_fn("gtg_gemm_bf16_grouped")(_ptr(x), x.stride(0), x.stride(1), None, 0, _ptr(w), K, N * K, None, _ptr(out),
+                                            out.stride(0), out.stride(1), 0, heads, M, N, K, 128 if M > 64 else 64,
+                                            2 if gate is not None else 0, *g, _stream()), "linear_heads(bfloat16)")
         return
     _check(_fn("gtg_gemm_simt_batched")(_dt(x), _ptr(x), x.stride(0), x.stride(1), _ptr(w), K, N * K, _ptr(out),
                                         out.stride(0), out.stride(1), heads, M, N, K, _stream()), "linear_heads")
+    if gate is not None:
+        for h in range(heads):
+            sigmoid_gate(out[:, h], gate[:, h])
 
 
 def linear_add_residual(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) -> bool:
@@ -949,6 +973,34 @@ def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], cos_sin: torch.
            "latent_prepare")
 
 
+def latent_attention_supports(kv, rank: int) -> bool:
+    """Whether the tensor-core attention over latent rows takes this cache entry:
+    bfloat16 rows of a multiple of 16 channels, a multiple of 8 (up to 512) of them values."""
+    return (kv is not None and kv.k.dtype == torch.bfloat16 and kv.n_kv_heads == 1 and kv.page_stride % 8 == 0
+            and bool(_fn("gtg_latent_attention_supports")(kv.head_dim, int(rank))))
+
+
+def latent_attention_bf16(q: torch.Tensor, out: torch.Tensor, kv, cu_seqlens, slots, start_pos, n_seqs: int,
+                          max_q_len: int, n_heads: int, rank: int, scale: float, window: int = 0) -> None:
+    """Attention of every (token, head) of the step over its sequence's cache rows
+    (one shared head of kv.head_dim channels, the first `rank` of which are the
+    values): q [N, heads * head_dim] folded query rows, out [N, heads * rank].
+    Causal, over the last `window` keys (0: all).  Prompts, portions and single
+    tokens alike."""
+    _rows2d(q, "latent_attention: q"); _rows2d(out, "latent_attention: out")
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and latent_attention_supports(kv, rank),
+          "latent_attention_bf16: bfloat16 rows of a multiple of 16 channels, a multiple of 8 of them values")
+    _need(q.shape[1] == n_heads * kv.head_dim and out.shape[1] == n_heads * rank and q.stride(0) % 8 == 0
+          and out.stride(0) % 2 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 4 == 0,
+          "latent_attention_bf16: q [N, heads * head_dim] and out [N, heads * rank], aligned rows")
+    _int32("latent_attention_bf16", cu_seqlens, slots, start_pos)
+    _check_access("latent_attention_bf16", 2, kv, slots, start_pos=start_pos, cu_seqlens=cu_seqlens, n_items=n_seqs)
+    _check(_fn("gtg_latent_attention_bf16")(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), kv.page_stride,
+                                            _ptr(kv.block_table), kv.table_stride, _ptr(cu_seqlens), _ptr(slots), _ptr(start_pos),
+                                            int(n_seqs), int(max_q_len), n_heads, kv.head_dim, int(rank), float(scale), int(window),
+                                            _stream()), "latent_attention_bf16")
+
+
 # ------------------------------------------------------------------ routed experts
 MOE_TILE_ROWS = 64
 
@@ -987,18 +1039,39 @@ def moe_arrange(chosen: torch.Tensor, n_experts: int, row_item: torch.Tensor, it
                                   _stream()), "moe_arrange")
 
 
+def moe_product_fused_supports(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether `moe_product` runs these operands on the tensor cores (where it can
+    apply the gated silu in its epilogue)."""
+    return w.dim() == 3 and _grouped_ok(a, w, w.shape[2], a.stride(0), w.shape[1] * w.shape[2])
+
+
 def moe_product(a: torch.Tensor, row_item: torch.Tensor, item_div: int, w: torch.Tensor, tile_expert: torch.Tensor,
-                out: torch.Tensor) -> None:
+                out: torch.Tensor, epilogue: str = "none") -> None:
     """out[row, :] = a[source(row), :] . w[expert of the row's tile]^T over arranged
     rows.  item_div > 0: the source is the pair's token, row_item[row] // item_div
-    (a holds tokens); 0: the row itself (a holds arranged rows).  w [E, N, K]."""
+    (a holds tokens); 0: the row itself (a holds arranged rows).  w [E, N, K].
+    The tile is out's rows over tile_expert's length: 64, or 128 on the tensor
+    cores.  epilogue="swiglu" (tensor cores only: `moe_product_fused_supports`):
+    every w[e] is laid out by `interleave_gate_up` and out [rows, N/2] = silu(gate) * up."""
     _rows2d(a, "moe_product: a"); _rows2d(out, "moe_product: out")
     E, N, K = w.shape
     cap = tile_expert.numel()
+    tile = out.shape[0] // max(cap, 1)
+    _need(epilogue in ("none", "swiglu"), f"moe_product: unknown epilogue {epilogue!r}")
+    n_out = N // 2 if epilogue == "swiglu" else N
     _need(w.is_contiguous() and a.dtype == w.dtype and a.shape[1] == K, "moe_product: a [*, K] and contiguous w [E, N, K] of one dtype")
-    _need(tuple(out.shape) == (cap * MOE_TILE_ROWS, N) and out.dtype in (a.dtype, torch.float32), "moe_product: out must be [tiles * 64, N]")
+    _need(tuple(out.shape) == (cap * tile, n_out) and out.dtype in (a.dtype, torch.float32), "moe_product: out must be [tiles * tile, N]")
     _need(item_div > 0 or a.shape[0] == out.shape[0], "moe_product: a must hold the arranged rows")
     _int32("moe_product", row_item, tile_expert)
+    if moe_product_fused_supports(a, w):
+        _need(tile in (64, 128), f"moe_product: tiles of 64 or 128 rows, not {tile}")
+        _need(epilogue == "none" or N % 16 == 0, "moe_product: the fused gated silu needs a multiple of 16 rows per expert")
+        _check(_fn("gtg_gemm_bf16_grouped")(_ptr(a), a.stride(0), 0, _ptr(row_item), int(item_div), _ptr(w), K, N * K,
+                                            _ptr(tile_expert), _ptr(out), out.stride(0), 0, 1 if out.dtype == torch.float32 else 0,
+                                            1, cap * tile, N, K, tile, 1 if epilogue == "swiglu" else 0, None, 0, 0, _stream()),
+               "moe_product(bfloat16)")
+        return
+    _need(epilogue == "none" and tile == MOE_TILE_ROWS, "moe_product: the plain product has tiles of 64 rows and no epilogue")
     _check(_fn("gtg_moe_product_simt")(_dt(a), 1 if out.dtype == torch.float32 else 0, _ptr(a), a.stride(0), _ptr(row_item),
                                        int(item_div), _ptr(w), K, N * K, _ptr(tile_expert), cap, _ptr(out), out.stride(0), N, K,
                                        _stream()), "moe_product")

@@ -150,9 +150,12 @@ class RoutedExperts(FeedForward):
     def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
         self.router = rt.vector(tensors[self.names["router"]])
         self.router_bias = rt.vector(tensors[self.router_bias_name]) if self.router_bias_name else None
-        # [E, 2I, H]: an expert's gate rows, then its up rows; [E, H, I]
-        self.w_gate_up = rt.matrix(torch.stack([torch.cat([tensors[self._name("gate", e)].to(rt.dtype),
-                                                           tensors[self._name("up", e)].to(rt.dtype)], dim=0)
+        # [E, 2I, H]: an expert's gate rows, then its up rows -- or, where the products run on the
+        # tensor cores and apply the gated silu in their epilogue, alternating in blocks of 8; [E, H, I]
+        self.fused = rt.dtype == torch.bfloat16 and self.inter % 8 == 0 and self.hidden % 8 == 0
+        both = (lambda g, u: ops.interleave_gate_up(g, u)) if self.fused else (lambda g, u: torch.cat([g, u], dim=0))
+        self.w_gate_up = rt.matrix(torch.stack([both(tensors[self._name("gate", e)].to(rt.dtype),
+                                                     tensors[self._name("up", e)].to(rt.dtype))
                                                 for e in range(self.n_experts)]))
         self.w_down = rt.matrix(torch.stack([tensors[self._name("down", e)].to(rt.dtype) for e in range(self.n_experts)]))
 
@@ -163,16 +166,22 @@ class RoutedExperts(FeedForward):
         weights = rt.empty(n, top, dtype=torch.float32)
         ops.moe_route(x, self.router, self.router_bias, chosen, weights)
         ctx.trace("experts", chosen)
-        tiles = ops.moe_tiles_cap(n * top, E)
-        rows = tiles * ops.MOE_TILE_ROWS
+        fused = self.fused and ops.moe_product_fused_supports(x, self.w_gate_up)
+        # tiles of 128 rows once the experts have that many tokens each on average
+        tile = 128 if fused and n * top >= 128 * E else ops.MOE_TILE_ROWS
+        tiles = ops.moe_tiles_cap(n * top, E, tile)
+        rows = tiles * tile
         row_item = rt.empty(rows, dtype=torch.int32)
         item_row = rt.empty(n * top, dtype=torch.int32)
         tile_expert = rt.empty(tiles, dtype=torch.int32)
-        ops.moe_arrange(chosen, E, row_item, item_row, tile_expert)
-        sums = rt.empty(rows, 2 * self.inter, dtype=torch.float32)
-        ops.moe_product(x, row_item, top, self.w_gate_up, tile_expert, sums)
+        ops.moe_arrange(chosen, E, row_item, item_row, tile_expert, tile)
         act = rt.empty(rows, self.inter)
-        ops.swiglu_bias(sums, None, None, act)
+        if fused:
+            ops.moe_product(x, row_item, top, self.w_gate_up, tile_expert, act, epilogue="swiglu")
+        else:
+            sums = rt.empty(rows, 2 * self.inter, dtype=torch.float32)
+            ops.moe_product(x, row_item, top, self.w_gate_up, tile_expert, sums)
+            ops.swiglu_bias(sums, None, None, act)
         y = rt.empty(rows, self.hidden, dtype=torch.float32)
         ops.moe_product(act, row_item, 0, self.w_down, tile_expert, y)
         out = rt.empty(n, self.hidden, dtype=torch.float32 if ctx.float_updates else None)

@@ -124,11 +124,15 @@ class LatentAttention(Mixer):
                          folded.view(n, H, self.row)[:, :, : self.rank])
         ctx.trace("q_attn", folded)
         attended = rt.empty(n, H * self.rank)
-        ops.attention_simple(folded, attended, kv, ctx.token_seq, ctx.slots, ctx.positions, H, self.scale,
-                             self.window or 0, value_dim=self.rank)
+        if rt.dtype == torch.bfloat16 and ops.latent_attention_supports(kv, self.rank):
+            ops.latent_attention_bf16(folded, attended, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, ctx.n_seqs,
+                                      ctx.max_q_len, H, self.rank, self.scale, self.window or 0)
+        else:
+            # float32, and row sizes the tensor-core kernel does not take
+            ops.attention_simple(folded, attended, kv, ctx.token_seq, ctx.slots, ctx.positions, H, self.scale,
+                                 self.window or 0, value_dim=self.rank)
         heads = rt.empty(n, (H * self.v_dim + 7) // 8 * 8)[:, : H * self.v_dim]
-        ops.linear_heads(attended.view(n, H, self.rank), self.w_uv, heads.view(n, H, self.v_dim))
-        if gate is not None:
-            ops.sigmoid_gate(heads, gate)
+        ops.linear_heads(attended.view(n, H, self.rank), self.w_uv, heads.view(n, H, self.v_dim),
+                         gate.view(n, H, self.v_dim) if gate is not None else None)
         ctx.trace("attn", heads)
         return emit_update(heads, self.w_o, ctx)
