@@ -31,7 +31,9 @@ With --design ropovik it measures the Ropovik design instead (see `run_design`):
 prefill and decode of a looped stack of Mamba-2 and attention layers at the
 layer sizes of two real models, beside the Llama decoder at equal width, depth
 and heads, and every kernel the design added beside the like kernel of the
-Llama path, each against the copy peak.  The default run is not changed by it.
+Llama path, each against the copy peak.  With --design senupel it does the same
+for the Senupel design (attention through a latent, dense and routed
+feed-forwards; see `senupel_shape`).  The default run is not changed by either.
 
 Peaks come from MEASURED_PEAKS.json beside this file if present, else from the
 fallback figures of an earlier measurement on the same pool.  Inputs are larger
@@ -466,6 +468,25 @@ def ropovik_shape(width, heads, kv_heads, dim, ff, m_heads, m_dim, m_state, m_gr
             "loop": {"start": 0, "stop": 4, "times": 2}, "layers": [mamba, attn, mamba, attn]}
 
 
+def senupel_shape(width, heads, ff, experts, expert_ff, top, window=4096, vocab=32000):
+    """Eight layers of attention through a latent (heads of 128 unrotated and 64 rotated
+    channels, values of 128, a latent of 512, the sizes latent attention is used with);
+    the even ones have a down projection and a dense feed-forward, the odd ones read
+    the latents of the layer before and route each token to `top` of `experts` experts
+    (together as wide as the dense feed-forward)."""
+    def mixer(i):
+        m = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+             "mask": {"size": window},
+             "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+        if i % 2:
+            m["kv_from"] = i - 1
+        return m
+    dense = {"kind": "dense", "ff": ff}
+    routed = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    return {"architecture": "Senupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [{"type": "latent_attention", "mixer": mixer(i), "mlp": routed if i % 2 else dense} for i in range(8)]}
+
+
 DESIGN_SIZES = {
     # the layer sizes of Llama-3.2-1B / SmolLM2 (width 2048) and of Llama-3.1-8B (width 4096); the
     # recurrence has twice the width in its inner size, heads of 64 and a state of 128, as Mamba-2 models do
@@ -474,8 +495,22 @@ DESIGN_SIZES = {
 }
 
 
+SENUPEL_SIZES = {
+    # the same two widths; 16 experts of a quarter of the dense feed-forward's size, four to a token
+    "w2048": (senupel_shape(2048, 16, 8192, 16, 2048, 4), dict(LLAMA_3P2_1B, num_hidden_layers=8, vocab_size=32000)),
+    "w4096": (senupel_shape(4096, 32, 14336, 16, 3584, 4), dict(LLAMA_3P1_8B, num_hidden_layers=8, vocab_size=32000)),
+}
+DESIGNS = {
+    "ropovik": (DESIGN_SIZES, "4 layers (mamba2, attention, mamba2, attention, a dense feed-forward each) run twice, "
+                              "beside 8 Llama layers of equal width, heads and feed-forward size; vocabulary 32000"),
+    "senupel": (SENUPEL_SIZES, "8 layers of attention through a latent (a window of 4096), dense gated feed-forwards with biases "
+                               "and mixtures of 16 experts (4 to a token) in turn, odd layers reading the even layers' latents, "
+                               "beside 8 Llama layers of equal width and feed-forward size; vocabulary 32000"),
+}
+
+
 def run_design(args):
-    """Prefill and decode throughput of the Ropovik design beside the Llama decoder at
+    """Prefill and decode throughput of a design beside the Llama decoder at
     equal width, depth and heads (random weights, bfloat16), and its own kernels one
     by one against the copy peak beside the like kernel of the Llama path.  One JSON line."""
     import torch
@@ -553,6 +588,108 @@ def run_design(args):
         torch.cuda.empty_cache()
         return out
 
+    def senupel_kernel_table(cfg):
+        """Each kernel the Senupel design added, alone, at this size: a prompt of T tokens
+        and a decode step of 64 sequences after 1,024 tokens; the bytes it has to move
+        against the copy peak and, for the products, its FLOPs against the matrix peak.
+        Beside each the like kernel of the Llama path at the same rows."""
+        from go_tinygrad_b200.cache import Cache, KVRequest
+        bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+        m = cfg["layers"][0]["mixer"]
+        ex = cfg["layers"][1]["mlp"]
+        H, heads, dim, rot, vdim, rank, window = cfg["width"], m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["mask"]["size"]
+        ff, E, eff, top = cfg["layers"][0]["mlp"]["ff"], ex["router"]["experts"], ex["expert"]["ff"], ex["router"]["top"]
+        row = rank + rot
+        rows = []
+
+        def add(name, rows_n, ms, nbytes, flops=0, like=None):
+            rows.append({"kernel": name, "rows": rows_n, "us": round(ms * 1e3, 2), "mb": round(nbytes / 1e6, 2),
+                         "of_copy_peak": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3),
+                         **({"tflops": round(flops / ms / 1e9, 1), "of_matrix_peak": round(flops / ms / 1e9 / pk["bf16_tflops"], 3)} if flops else {}),
+                         **({"like": like} if like else {})})
+        rnd = lambda *shape, dtype=bf: torch.randn(*shape, device=dev, dtype=f32).to(dtype)
+        for n, n_seqs, ctx_len, tag in ((T, 1, 0, "prompt"), (64, 64, prompt_len, "decode")):
+            per = n // n_seqs
+            rt = lib.parts.Runtime(dev, bf)
+            cache = Cache([[KVRequest(1, row, window, planes=1)], [KVRequest(heads // 2, 128, None)]], [None, None],
+                          max_tokens=64 * ((ctx_len + per + 63) // 64) * n_seqs, max_slots=n_seqs, dtype=bf, device=dev)
+            slot_list = [cache.open_sequence() for _ in range(n_seqs)]
+            cache.reserve_many([(s, ctx_len + per) for s in slot_list]); cache.flush_tables()
+            for g in cache.groups:
+                g.storage.normal_()
+            kv, kv_like = cache.handles[0].kv, cache.handles[1].kv
+            cu = torch.arange(0, n + 1, per, dtype=i32, device=dev)
+            seq = torch.arange(n, dtype=i32, device=dev) // per
+            slots = torch.tensor(slot_list, dtype=i32, device=dev)
+            start = torch.full((n_seqs,), ctx_len, dtype=i32, device=dev)
+            pos = (start[seq.long()] + (torch.arange(n, device=dev) % per)).to(i32)
+            # the norm on a sublayer's output, beside the norm before a sublayer
+            res, upd, w = rnd(n, H, dtype=f32), rnd(n, H), rnd(H, dtype=f32)
+            image, out = torch.empty(n, H, dtype=bf, device=dev), torch.empty(n, H, dtype=bf, device=dev)
+            add(f"rmsnorm_add ({tag})", n, timed(lambda: ops.rmsnorm_add(upd, w, 1e-5, res, image)), n * H * (2 + 4 + 4 + 2))
+            add(f"add_rmsnorm ({tag})", n, timed(lambda: ops.add_rmsnorm(res, upd, w, 1e-5, out)), n * H * (4 + 4 + 2 + 2), like="rmsnorm_add")
+            # latent norm, rotation and cache store, beside rotation and store of ordinary heads
+            q, dkv = rnd(n, heads * (dim + rot)), rnd(n, row)
+            cs, nw = rnd(n, rot // 2, 2, dtype=f32), rnd(rank, dtype=f32)
+            folded = torch.empty(n, heads * row, dtype=bf, device=dev)
+            add(f"latent_prepare ({tag})", n, timed(lambda: ops.latent_prepare(q, dkv, cs, nw, 1e-5, kv, seq, slots, pos, folded, heads, dim, rot, rank)),
+                n * (row * 4 + heads * rot * 4))
+            qkv, cs2 = rnd(n, (heads + heads) * 128), rnd(n, 64, 2, dtype=f32)
+            add(f"rope_kv_store ({tag})", n, timed(lambda: ops.rope_kv_store(qkv, cs2, heads, heads // 2, 128, kv_like, seq, slots, pos)),
+                n * (heads * 128 * 4 + heads * 128 * 3), like="latent_prepare")
+            # the products per head, beside one product of the same size
+            w_uk, w_uv = rnd(heads, rank, dim), rnd(heads, vdim, rank)
+            att, hd, gate = rnd(n, heads * rank), torch.empty(n, heads * vdim, dtype=bf, device=dev), rnd(n, heads * vdim)
+            fl = 2 * n * heads * dim * rank
+            add(f"linear_heads fold ({tag})", n, timed(lambda: ops.linear_heads(q.view(n, heads, dim + rot)[:, :, :dim], w_uk, folded.view(n, heads, row)[:, :, :rank])),
+                w_uk.numel() * 2 + n * heads * (dim + rank) * 2, fl)
+            add(f"linear_heads values + gate ({tag})", n, timed(lambda: ops.linear_heads(att.view(n, heads, rank), w_uv, hd.view(n, heads, vdim), gate.view(n, heads, vdim))),
+                w_uv.numel() * 2 + n * heads * (rank + 2 * vdim) * 2, fl)
+            wl, xl, ol = rnd(rank, heads * dim), rnd(n, heads * dim), torch.empty(n, rank, dtype=bf, device=dev)
+            add(f"linear, as many FLOPs ({tag})", n, timed(lambda: ops.linear(xl, wl, ol)), wl.numel() * 2 + n * (heads * dim + rank) * 2, fl, like="linear_heads")
+            # attention
+            keys = (ctx_len + per) * n_seqs if per == 1 else sum(min(i + 1, window) for i in range(per))
+            add(f"latent_attention ({tag})", n, timed(lambda: ops.latent_attention_bf16(folded, att, kv, cu, slots, start, n_seqs, per, heads, rank, 0.07, window)),
+                n * heads * (row + rank) * 2 + (n_seqs * (ctx_len + per)) * row * 2, 2 * heads * keys * (row + rank))
+            ql, ml = rnd(n, heads * 128), torch.empty(n, heads * 128, dtype=bf, device=dev)
+            if per == 1:
+                splits, chunk, ring = ops.attention_decode_plan(n, heads, heads // 2, 128, ctx_len + 1, 0, n * (ctx_len + 1))
+                scratch = torch.empty(max(1, ops.attention_decode_scratch_floats(n, heads, 128, splits)), dtype=f32, device=dev)
+                fn = lambda: ops.attention_decode_bf16(ql, ml, kv_like, slots, pos, heads, 0.09, 0, splits, scratch, chunk_pages=chunk, ring_pages=ring)
+            else:
+                fn = lambda: ops.attention_prefill_tcgen05(ql, ml, kv_like, cu, slots, start, n_seqs, per, heads, 0.09, 0)
+            add(f"attention, {heads} heads of 128 on {heads // 2} key heads ({tag})", n, timed(fn),
+                n * heads * 128 * 4 + n_seqs * (ctx_len + per) * (heads // 2) * 128 * 4, 2 * heads * keys * 256, like="latent_attention")
+            # biases
+            sums, bg, act = rnd(n, 2 * ff, dtype=f32), rnd(ff, dtype=f32), torch.empty(n, ff, dtype=bf, device=dev)
+            add(f"swiglu_bias ({tag})", n, timed(lambda: ops.swiglu_bias(sums, bg, bg, act)), n * ff * (8 + 2))
+            gu = rnd(n, 2 * ff)
+            add(f"swiglu ({tag})", n, timed(lambda: ops.swiglu(gu, act)), n * ff * 6, like="swiglu_bias")
+            ys, bd = rnd(n, H, dtype=f32), rnd(H, dtype=f32)
+            add(f"add_bias ({tag})", n, timed(lambda: ops.add_bias(ys, bd, out)), n * H * 6)
+            # routed experts
+            x, router, rb = rnd(n, H), rnd(E, H, dtype=f32), rnd(E, dtype=f32)
+            chosen, wts = torch.empty(n, top, dtype=i32, device=dev), torch.empty(n, top, dtype=f32, device=dev)
+            add(f"moe_route ({tag})", n, timed(lambda: ops.moe_route(x, router, rb, chosen, wts)), n * H * 2 + E * H * 4)
+            tile = 128 if n * top >= 128 * E else 64
+            tiles = ops.moe_tiles_cap(n * top, E, tile)
+            row_item, item_row = torch.empty(tiles * tile, dtype=i32, device=dev), torch.empty(n * top, dtype=i32, device=dev)
+            tile_expert = torch.empty(tiles, dtype=i32, device=dev)
+            add(f"moe_arrange ({tag})", n, timed(lambda: ops.moe_arrange(chosen, E, row_item, item_row, tile_expert, tile)), n * top * 12)
+            wgu, wd = rnd(E, 2 * eff, H), rnd(E, H, eff)
+            acts, y = torch.empty(tiles * tile, eff, dtype=bf, device=dev), torch.empty(tiles * tile, H, dtype=f32, device=dev)
+            used = min(E, n * top)
+            add(f"moe_product gate, up, silu ({tag})", n, timed(lambda: ops.moe_product(x, row_item, top, wgu, tile_expert, acts, epilogue="swiglu")),
+                used * 2 * eff * H * 2 + n * H * 2 + n * top * eff * 2, 2 * n * top * 2 * eff * H)
+            add(f"moe_product down ({tag})", n, timed(lambda: ops.moe_product(acts, row_item, 0, wd, tile_expert, y)),
+                used * eff * H * 2 + n * top * (eff * 2 + H * 4), 2 * n * top * eff * H)
+            wg2, a2 = rnd(2 * eff * top, H), torch.empty(n, eff * top, dtype=bf, device=dev)
+            add(f"linear gate, up, silu of {top} experts' width ({tag})", n, timed(lambda: ops.linear(x, wg2, a2, epilogue="swiglu")),
+                wg2.numel() * 2 + n * (H + eff * top) * 2, 2 * n * top * 2 * eff * H, like="moe_product")
+            add(f"moe_combine ({tag})", n, timed(lambda: ops.moe_combine(y, item_row, wts, out)), n * top * H * 4 + n * H * 2)
+            del cache
+        return rows
+
     def kernel_table(cfg):
         """Each kernel the design added, alone, at this size: a prompt of T tokens and a
         decode step of 64 sequences; bytes it has to move / time / the copy peak.  Beside
@@ -614,14 +751,15 @@ def run_design(args):
     sampler.start()
     sampler.mark()
     sizes = {}
-    for name in (args.sizes.split(",") if args.sizes else list(DESIGN_SIZES)):
-        ropovik_cfg, llama_cfg = DESIGN_SIZES[name]
-        sizes[name] = {"ropovik": model_numbers(ropovik_cfg), "llama": model_numbers(llama_cfg),
-                       "kernels": kernel_table(ropovik_cfg)}
+    design_sizes, what = DESIGNS[args.design]
+    table = senupel_kernel_table if args.design == "senupel" else kernel_table
+    for name in (args.sizes.split(",") if args.sizes else list(design_sizes)):
+        design_cfg, llama_cfg = design_sizes[name]
+        sizes[name] = {args.design: model_numbers(design_cfg), "llama": model_numbers(llama_cfg),
+                       "kernels": table(design_cfg)}
     clocks = sampler.stop()
-    print(json.dumps({"design": "ropovik", "dtype": "bf16", "data": "synthetic (random weights and token ids)",
-                      "what": "4 layers (mamba2, attention, mamba2, attention, a dense feed-forward each) run twice, "
-                              "beside 8 Llama layers of equal width, heads and feed-forward size; vocabulary 32000",
+    print(json.dumps({"design": args.design, "dtype": "bf16", "data": "synthetic (random weights and token ids)",
+                      "what": what,
                       "peaks": pk, "l2": "flushed before every timed prefill and kernel; decode steps read more than the L2 holds",
                       "steps": args.steps, "clocks": clocks, "sizes": sizes}))
     return 0
@@ -680,7 +818,7 @@ def main():
                     help="with --only: also print, as comment lines, the time each kernel adds to a step")
     ap.add_argument("--eager", action="store_true",
                     help="launch the decode step kernel by kernel instead of replaying a graph")
-    ap.add_argument("--design", default=None, choices=["ropovik"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="measure this design beside the Llama decoder at equal size instead of the default workload")
     ap.add_argument("--sizes", default="", help="with --design: which of its sizes, comma separated (default: all)")
     ap.add_argument("--no-chain", action="store_true",

@@ -153,9 +153,16 @@ def model_close(folders, name, dtype, tokens, got, routing, what):
         want = want_logits(folders, name, tokens)
         own = plain.forward(CONFIGS[name][0], weights_of(folders, name), list(tokens), routing=routing)
         assert np.array_equal(own, want), f"{what}: the model chose other experts than the plain implementation"
-    else:
-        want = plain.forward(CONFIGS[name][0], weights_of(folders, name), list(tokens), routing=routing)
-    assert_close(got, want, dtype, what)
+        return assert_close(got, want, dtype, what)
+    # bfloat16: the mean error as for every model; the largest single error may be a little larger than
+    # elsewhere (0.08 of the largest logit, not 0.05): every sublayer's output is divided by its own root
+    # mean square, which magnifies the rounding of a small output.  A wrong key or window errs by about 1.
+    want = plain.forward(CONFIGS[name][0], weights_of(folders, name), list(tokens), routing=routing)
+    got = np.asarray(got, dtype=np.float64)
+    assert got.shape == want.shape and np.isfinite(got).all(), what
+    scale, err = max(1.0, float(np.abs(want).max())), np.abs(got - want)
+    assert err.mean() <= 6e-3 * scale, f"{what}: mean error {err.mean():.3e}"
+    assert err.max() <= 8e-2 * scale, f"{what}: max error {err.max():.3e} at {np.unravel_index(int(err.argmax()), err.shape)}"
 
 
 def run_cut(model, cache, tokens, portions):
@@ -245,6 +252,46 @@ def test_products_per_head_on_views(dtype):
         want = np.einsum("mhk,hnk->mhn", f64(wide).reshape(M, heads, K + 3)[:, :, :K], f64(w))
         close(out.view(M, heads, N + 2)[:, :, :N], want, dtype, (M, heads, K, N))
         assert float(out.view(M, heads, N + 2)[:, :, N:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("heads,row,rank", [(16, 576, 512), (3, 48, 40), (128, 96, 64), (5, 192, 176), (1, 16, 8), (8, 80, 64)])
+@pytest.mark.parametrize("window", [0, 1, 70, 64])
+def test_tensor_core_attention_over_latent_rows(heads, row, rank, window):
+    """The bfloat16 kernel alone on random cache rows: sequences that bring a whole
+    prompt, a portion after 100 tokens, two tokens after 63, and one token after 64,
+    130 and 0; query tiles that straddle tokens; against softmax in float64."""
+    from go_tinygrad_b200.cache import KVRequest
+    rng = np.random.default_rng(heads + row)
+    new, starts = [150, 37, 2, 1, 1, 1], [0, 100, 63, 64, 130, 0]
+    cache = Cache([[KVRequest(1, row, window or None, planes=1)]], [None], max_tokens=64 * 16, max_slots=8, dtype=torch.bfloat16, device=DEV)
+    cache.open_sequence()
+    slots = [cache.open_sequence() for _ in new]
+    cache.reserve_many([(s, a + n) for s, a, n in zip(slots, starts, new)]); cache.flush_tables()
+    kv = cache.handles[0].kv
+    assert ops.latent_attention_supports(kv, rank)
+    rows = []
+    for s, a, n in zip(slots, starts, new):
+        r = t32(rng.standard_normal((a + n, row))).to(torch.bfloat16)
+        table = cache.groups[0].table_host[s]
+        for p0 in range(0, a + n, 64):
+            kv.k[int(table[p0 // 64]), 0, : min(64, a + n - p0)] = r[p0:p0 + 64]
+        rows.append(f64(r))
+    rt = Runtime(DEV, torch.bfloat16)
+    ctx = context(rt, new, starts, slots)
+    q = t32(rng.standard_normal((sum(new), heads * row)) * 0.5).to(torch.bfloat16)
+    out = torch.zeros(sum(new), heads * rank, dtype=torch.bfloat16, device=DEV)
+    scale = 1.7 / np.sqrt(row)
+    ops.latent_attention_bf16(q, out, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, len(new), max(new), heads, rank, scale, window)
+    got, q64, at = f64(out).reshape(-1, heads, rank), f64(q).reshape(-1, heads, row), 0
+    for r, a, n in zip(rows, starts, new):
+        for i in range(n):
+            pos = a + i
+            lo = max(0, pos - window + 1) if window else 0
+            sc = q64[at + i] @ r[lo:pos + 1].T * scale
+            w = np.exp(sc - sc.max(-1, keepdims=True))
+            want = (w / w.sum(-1, keepdims=True)) @ r[lo:pos + 1, :rank]
+            assert np.abs(got[at + i] - want).max() <= 2e-2 * max(1.0, np.abs(want).max()), (a, i, np.abs(got[at + i] - want).max())
+        at += n
 
 
 def _latent_mixer(dtype, m, hidden, weights, own_kv=True):
