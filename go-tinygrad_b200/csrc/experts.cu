@@ -14,12 +14,18 @@
 //            computed by itself.
 //   product  C[row,:] = A[source(row),:] . W[expert(row)]^T, tiles of 64 rows,
 //            one accumulator per output walking k in order.
+//   gather   G[row,:] = x[token of row_item[row],:] (zeros for padding): the arranged
+//            copy of the inputs that a product fed by tensor copies reads.
 //   combine  out[t,:] = sum_k weight[t,k] * Y[item_row[t*top+k],:], k in order.
 #include "common.cuh"
 #include <math.h>
 
 namespace {
 // ---- route ----------------------------------------------------------------------
+// One block of four warps per token: the token's row is staged in shared memory as
+// float, every warp takes every fourth pair of experts (two dot products at a time,
+// lanes striding over the channels, the router's rows read coalesced), and thread 0
+// picks from the logits.
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, const float* __restrict__ bias,
@@ -27,20 +33,32 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
     chain_release();
     chain_wait();
     extern __shared__ float smem[];
+    float* xs = smem;            // [H]
+    float* z = smem + H;         // [E]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * 4 + warp;
-    if (n >= N) return;
-    float* z = smem + (size_t)warp * E;
+    const int n = blockIdx.x;
     const T* xr = x + (size_t)n * ldx;
-    for (int e = 0; e < E; ++e) {
-        const float* r = router + (size_t)e * H;
-        float s = 0.f;
-        for (int i = lane; i < H; i += 32) s = fmaf(to_f32<T>(xr[i]), r[i], s);
-        s = warp_sum(s);
-        if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = to_f32<T>(xr[i]);
+    __syncthreads();
+    for (int e = 2 * warp; e < E; e += 8) {
+        const bool two = e + 1 < E;
+        const float* r0 = router + (size_t)e * H;
+        const float* r1 = router + (size_t)(two ? e + 1 : e) * H;
+        float s0 = 0.f, s1 = 0.f;
+        for (int i = lane; i < H; i += 32) {
+            const float v = xs[i];
+            s0 = fmaf(v, r0[i], s0);
+            s1 = fmaf(v, r1[i], s1);
+        }
+        s0 = warp_sum(s0);
+        s1 = warp_sum(s1);
+        if (lane == 0) {
+            z[e] = s0 + (bias ? bias[e] : 0.f);
+            if (two) z[e + 1] = s1 + (bias ? bias[e + 1] : 0.f);
+        }
     }
-    __syncwarp();
-    if (lane == 0) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
         float best0 = 0.f, total = 0.f;
         for (int k = 0; k < top; ++k) {
             int arg = -1;
@@ -164,6 +182,17 @@ grouped_simt_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ r
     }
 }
 
+// ---- gather -------------------------------------------------------------------------
+__global__ void moe_gather_kernel(const bf16* __restrict__ x, int ldx, const int* __restrict__ row_item, int item_div,
+                                  bf16* __restrict__ out, int H8) {
+    chain_release();
+    chain_wait();
+    const int item = row_item[blockIdx.x];
+    const uint4* src = item < 0 ? nullptr : reinterpret_cast<const uint4*>(x + (size_t)(item / item_div) * ldx);
+    uint4* dst = reinterpret_cast<uint4*>(out) + (size_t)blockIdx.x * H8;
+    for (int i = threadIdx.x; i < H8; i += blockDim.x) dst[i] = src ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+}
+
 // ---- combine ----------------------------------------------------------------------
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, int ldy, const int* __restrict__ item_row,
@@ -184,9 +213,9 @@ GTG_API int gtg_moe_route(int dtype, const void* x, int ldx, const float* router
                           float* weights, int N, int H, int E, int top, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || H <= 0) return kErrBadArgument;
-    const size_t smem = (size_t)4 * E * sizeof(float);
+    const size_t smem = (size_t)(H + E) * sizeof(float);
     if (smem > 48 * 1024) return kErrUnsupported;
-    const dim3 grid((N + 3) / 4);
+    const dim3 grid(N);
     if (dtype == 0) return launch_chained(moe_route_kernel<float>, grid, dim3(128), smem, stream, (const float*)x, ldx, router, bias, chosen, weights, N, H, E, top);
     if (dtype == 1) return launch_chained(moe_route_kernel<bf16>, grid, dim3(128), smem, stream, (const bf16*)x, ldx, router, bias, chosen, weights, N, H, E, top);
     return kErrBadArgument;
@@ -227,6 +256,15 @@ GTG_API int gtg_moe_product_simt(int dtype, int c_f32, const void* A, int lda, c
         return launch_chained(grouped_simt_kernel<bf16, bf16, bf16>, grid, dim3(256), 0, stream, (const bf16*)A, lda, row_item,
                               item_div, (const bf16*)W, ldw, expert_stride, tile_expert, (bf16*)C, ldc, N, K);
     return kErrBadArgument;
+}
+
+// out[row, :] = x[row_item[row] / item_div, :], zeros where row_item[row] < 0 (bfloat16 rows of a multiple of 8 channels).
+GTG_API int gtg_moe_gather(const void* x, int ldx, const int* row_item, int item_div, void* out, int rows, int H,
+                           cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (H <= 0 || item_div <= 0) return kErrBadArgument;
+    if (H % 8 || ldx % 8 || ((uintptr_t)x % 16) || ((uintptr_t)out % 16)) return kErrUnsupported;
+    return launch_chained(moe_gather_kernel, dim3(rows), dim3(128), 0, stream, (const bf16*)x, ldx, row_item, item_div, (bf16*)out, H / 8);
 }
 
 GTG_API int gtg_moe_combine(int dtype, const float* y, int ldy, const int* item_row, const float* weights, void* out,

@@ -155,11 +155,19 @@ struct RopeKV {
     int n_heads, n_kv;
 };
 
+// For products over rows arranged by expert (a mixture of experts): tile m of 128 rows of A
+// is multiplied with the matrix of expert tile_expert[m], whose rows lie expert_rows * expert
+// further down in W; a tile whose entry is negative does not exist and is skipped by every role.
+struct Grouping {
+    const int* tile_expert;      // null: one W for all rows
+    int expert_rows;
+};
+
 template <typename OutT, bool kTest>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_c, int use_store_map,
-                    OutT* __restrict__ C, int ldc, int M, int N, int K, int epi_code, RopeKV rope) {
+                    OutT* __restrict__ C, int ldc, int M, int N, int K, int epi_code, RopeKV rope, Grouping grp) {
     // a code from kEpiActivation on is the plain product (0) with a pointwise activation on its sums
     const int act = epi_code >= kEpiActivation ? epi_code - kEpiActivation + 1 : 0;
     const int epi = act ? 0 : epi_code;
@@ -206,6 +214,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+                int w_row = n0;
+                if (grp.tile_expert) {
+                    const int expert = grp.tile_expert[tile % tiles_m];
+                    if (expert < 0) continue;
+                    w_row += expert * grp.expert_rows;
+                }
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
@@ -213,7 +227,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (!ok) break;
                     mbar_expect_tx(full_bar(s), kStageBytes);
                     tma_load_2d<kTest>(base + s * kStageBytes, &map_a, kb * BK, m0, full_bar(s));
-                    tma_load_2d<kTest>(base + s * kStageBytes + kABytes, &map_w, kb * BK, n0, full_bar(s));
+                    tma_load_2d<kTest>(base + s * kStageBytes + kABytes, &map_w, kb * BK, w_row, full_bar(s));
                 }
             }
         }
@@ -224,7 +238,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t it = 0;
             bool ok = true;
             int t = 0;                                         // tiles done by this CTA
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                if (grp.tile_expert && grp.tile_expert[tile % tiles_m] < 0) continue;
                 const int acc = t & 1;
                 ok = mbar_wait<kTest>(acc_empty_bar(acc), (((uint32_t)t >> 1) & 1u) ^ 1u, abort_flag);   // epilogue drained it
                 if (!ok) break;
@@ -244,6 +259,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     umma_commit(empty_bar(s));                  // the stage is free once these MMAs have read it
                 }
                 umma_commit(acc_full_bar(acc));                 // this accumulator is complete
+                ++t;
             }
         }
     } else {
@@ -257,7 +273,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         unsigned char* stage_base = aligned + STAGES * kStageBytes + 1024 + warp * (2 * kStoreBytes);
         uint32_t groups = 0;                               // 64-column boxes stored so far by this warp
         int t = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            if (grp.tile_expert && grp.tile_expert[tile % tiles_m] < 0) continue;
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
             const int acc = t & 1;
             if (!mbar_wait<kTest>(acc_full_bar(acc), ((uint32_t)t >> 1) & 1u, abort_flag)) break;
@@ -467,6 +484,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+            ++t;
         }
         if ((staged || epi == 3) && lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");   // stores have landed
     }
@@ -520,7 +538,7 @@ GTG_API int gtg_gemm_bf16_tcgen05_status() {
 namespace {
 // epilogue 0: C[M,N] = A W^T.  1: SwiGLU over interleaved rows.  2: rotation and cache store (rope).
 int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_f32, int M, int N, int K,
-        int epilogue, const RopeKV& rope, cudaStream_t stream) {
+        int epilogue, const RopeKV& rope, cudaStream_t stream, const Grouping& grp = Grouping{nullptr, 0}, int n_experts = 1) {
     if (M <= 0 || N <= 0) return 0;
     const bool with_activation = epilogue >= kEpiActivation && epilogue < kEpiActivation + kActivations;
     if ((epilogue < 0 || epilogue > 3) && !with_activation) return kErrBadArgument;
@@ -533,7 +551,7 @@ int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int ou
     CUtensorMap map_a, map_w;
     int st = make_map(&map_a, A, M, K, lda, BM);
     if (st != 0) return st;
-    st = make_map(&map_w, W, N, K, ldw, BN);
+    st = make_map(&map_w, W, N * n_experts, K, ldw, BN);
     if (st != 0) return st;
     // the store map: C as [M, output width] bfloat16 in boxes of 64 x 32 (when its rows allow it)
     const int n_out = epilogue == 1 ? N / 2 : N;
@@ -576,15 +594,15 @@ int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int ou
     if (g_test_waits) {
         if (out_f32)
             return launch_chained(gemm_tcgen05_kernel<float, true>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
-                                  map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue, rope);
+                                  map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue, rope, grp);
         return launch_chained(gemm_tcgen05_kernel<bf16, true>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
-                              map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue, rope);
+                              map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue, rope, grp);
     }
     if (out_f32)
         return launch_chained(gemm_tcgen05_kernel<float, false>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
-                              map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue, rope);
+                              map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue, rope, grp);
     return launch_chained(gemm_tcgen05_kernel<bf16, false>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
-                          map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue, rope);
+                          map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue, rope, grp);
 }
 }  // namespace
 
@@ -596,6 +614,18 @@ GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw
     if (epilogue != 0 && epilogue != 1 && !(epilogue >= kEpiActivation && epilogue < kEpiActivation + kActivations))
         return kErrBadArgument;
     return run(A, lda, W, ldw, C, ldc, out_f32, M, N, K, epilogue, RopeKV{}, stream);
+}
+
+// The same over rows arranged by expert in tiles of 128: rows [128 t, 128 t + 128) of A meet
+// W[tile_expert[t]] (W holds n_experts matrices [N, K] one after the other); tiles whose entry
+// is negative are skipped.  M is the arranged rows, tile_expert has M / 128 entries.
+GTG_API int gtg_gemm_bf16_tcgen05_grouped(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
+                                          int out_f32, int M, int N, int K, int epilogue, const int* tile_expert,
+                                          int n_experts, cudaStream_t stream) {
+    if (epilogue != 0 && epilogue != 1) return kErrBadArgument;
+    if (!tile_expert || n_experts <= 0 || M % BM) return kErrBadArgument;
+    if ((long long)N * n_experts > 0x7fffffffLL) return kErrUnsupported;
+    return run(A, lda, W, ldw, C, ldc, out_f32, M, N, K, epilogue, RopeKV{}, stream, Grouping{tile_expert, N}, n_experts);
 }
 
 // residual[M,N] (float, row pitch ldr) += bfloat16(A W^T): the update, rounded as a

@@ -123,7 +123,8 @@ __global__ void __launch_bounds__(kLatThreads)
 latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
                             const bf16* __restrict__ kc, long long page_stride, const int* __restrict__ block_table,
                             int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
-                            const int* __restrict__ start_pos, int n_heads, int D, int rank, float scale, int window) {
+                            const int* __restrict__ start_pos, int n_heads, int D, int rank, float scale, int window,
+                            int n_splits, float* __restrict__ scratch, int total_rows) {
     chain_release();
     chain_wait();
     extern __shared__ __align__(128) unsigned char smem[];
@@ -142,6 +143,25 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
     int* row_pos = reinterpret_cast<int*>(part + 2 * 4 * kTileRows);                  // [32] position or -1
     const int start = start_pos[b];
     const int* table = block_table + (size_t)slots[b] * table_stride;
+    const int last_row = min(r0 + kTileRows, n_new * n_heads) - 1;
+    const int pos_min = start + r0 / n_heads, pos_max = start + last_row / n_heads;
+    const int lo_min = (window > 0 && pos_min - window + 1 > 0) ? pos_min - window + 1 : 0;
+    int page_lo = lo_min / kPageTokens, page_hi = pos_max / kPageTokens;
+    if (n_splits > 1) {
+        // the pages of the tile in n_splits equal runs; this block takes run blockIdx.z and leaves
+        // (maximum, sum, unnormalised values) of its rows in `scratch` for the merge kernel
+        const int chunk = (page_hi - page_lo + n_splits) / n_splits;
+        page_lo += blockIdx.z * chunk;
+        page_hi = min(page_hi, page_lo + chunk - 1);
+        if (page_lo > page_hi) {
+            if (tid < kTileRows && r0 + tid <= last_row) {
+                float* dst = scratch + ((size_t)blockIdx.z * total_rows + (size_t)tok0 * n_heads + r0 + tid) * (rank + 2);
+                dst[0] = -INFINITY;
+                dst[1] = 0.f;
+            }
+            return;
+        }
+    }
     if (tid < kTileRows) {
         const int r = r0 + tid;
         row_pos[tid] = r < n_new * n_heads ? start + r / n_heads : -1;
@@ -154,10 +174,6 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
         const bf16* src = ok ? q + (size_t)(tok0 + row / n_heads) * ldq + (size_t)(row % n_heads) * D + c * 8 : q;
         cp_async16(smem_u32(q_s + r * ldr + c * 8), src, ok ? 16 : 0);
     }
-    const int last_row = min(r0 + kTileRows, n_new * n_heads) - 1;
-    const int pos_min = start + r0 / n_heads, pos_max = start + last_row / n_heads;
-    const int lo_min = (window > 0 && pos_min - window + 1 > 0) ? pos_min - window + 1 : 0;
-    const int page_lo = lo_min / kPageTokens, page_hi = pos_max / kPageTokens;
 
     auto load_page = [&](int buf, int p) {
         const bf16* src = kc + (size_t)table[p] * page_stride;
@@ -292,6 +308,19 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
         }
     }
     cp_async_wait<0>();
+    if (n_splits > 1) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            if (pos_r[hh] < 0) continue;
+            float* dst = scratch + ((size_t)blockIdx.z * total_rows + (size_t)tok0 * n_heads + r0 + rg * 16 + g + hh * 8) * (rank + 2);
+            if (quarter == 0 && t == 0) { dst[0] = m_run[hh]; dst[1] = l_run[hh]; }
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+                if (j < my_tiles)
+                    *reinterpret_cast<float2*>(dst + 2 + (tile_lo + j) * 8 + t * 2) = make_float2(o[j][hh * 2], o[j][hh * 2 + 1]);
+        }
+        return;
+    }
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         const int row = r0 + rg * 16 + g + hh * 8;
@@ -302,6 +331,36 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
         for (int j = 0; j < NT; ++j)
             if (j < my_tiles)
                 *reinterpret_cast<__nv_bfloat162*>(dst + j * 8) = __floats2bfloat162_rn(o[j][hh * 2] * inv, o[j][hh * 2 + 1] * inv);
+    }
+}
+
+// out[row, :] = sum_z exp(m_z - M) O_z / sum_z exp(m_z - M) l_z, M = max_z m_z: the runs of a row's
+// keys brought together, z in order.
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out, int ldo, int n_heads, int rank,
+                              int n_splits, int total_rows) {
+    chain_release();
+    chain_wait();
+    const int row = blockIdx.x;
+    const size_t stride = (size_t)total_rows * (rank + 2);
+    const float* base = scratch + (size_t)row * (rank + 2);
+    float M = -INFINITY;
+    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, base[z * stride]);
+    if (M == -INFINITY) return;
+    float L = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+        const float m = base[z * stride];
+        if (m != -INFINITY) L += expf(m - M) * base[z * stride + 1];
+    }
+    const float inv = 1.0f / L;
+    bf16* dst = out + (size_t)(row / n_heads) * ldo + (size_t)(row % n_heads) * rank;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float acc = 0.f;
+        for (int z = 0; z < n_splits; ++z) {
+            const float m = base[z * stride];
+            if (m != -INFINITY) acc = fmaf(expf(m - M), base[z * stride + 2 + c], acc);
+        }
+        dst[c] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -316,10 +375,36 @@ GTG_API int gtg_latent_attention_supports(int D, int rank) {
     return D > 0 && D % 16 == 0 && rank > 0 && rank % 8 == 0 && rank <= 512 && rank <= D && latent_attention_smem(D) <= 220 * 1024;
 }
 
+// Into how many runs the keys of a tile are best cut, for a step of n_seqs sequences that bring
+// max_q_len tokens at most and reach max_kv_len keys at most: enough thread blocks for every
+// place on the device twice over, runs of two pages at least.  1 for prompts.
+GTG_API int gtg_latent_attention_splits(int n_seqs, int max_q_len, int n_heads, int D, int max_kv_len, int window) {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0, n = 0;
+        sms = (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+    }
+    const long long tiles = (((long long)max_q_len * n_heads + kTileRows - 1) / kTileRows) * n_seqs;
+    int keys = max_kv_len;
+    if (window > 0 && window + max_q_len < keys) keys = window + max_q_len;
+    const int pages = keys / kPageTokens + 1;
+    const size_t per_sm = (size_t)220 * 1024 / latent_attention_smem(D);
+    const long long places = 2LL * sms * (per_sm > 0 ? (long long)per_sm : 1);
+    long long splits = (places + tiles - 1) / tiles;
+    if (splits > pages / 2) splits = pages / 2;
+    if (splits > 32) splits = 32;
+    return splits < 1 ? 1 : (int)splits;
+}
+
+GTG_API long long gtg_latent_attention_scratch_floats(int total_rows, int rank, int n_splits) {
+    return n_splits > 1 ? (long long)n_splits * total_rows * (rank + 2) : 0;
+}
+
 GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo, const void* kc, long long page_stride,
                                       const int* block_table, int table_stride, const int* cu_seqlens, const int* slots,
                                       const int* start_pos, int n_seqs, int max_q_len, int n_heads, int D, int rank,
-                                      float scale, int window, cudaStream_t stream) {
+                                      float scale, int window, int n_splits, float* scratch, int n_tokens,
+                                      cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (n_heads <= 0) return kErrBadArgument;
     if (!gtg_latent_attention_supports(D, rank)) return kErrUnsupported;
@@ -327,7 +412,9 @@ GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo
     const size_t smem = latent_attention_smem(D);
     const long long tiles = ((long long)max_q_len * n_heads + kTileRows - 1) / kTileRows;
     if (tiles > 0x7fffffffLL || n_seqs > 65535) return kErrUnsupported;
-    const dim3 grid((unsigned)tiles, n_seqs);
+    if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && (!scratch || rank % 2))) return kErrBadArgument;
+    const dim3 grid((unsigned)tiles, n_seqs, n_splits);
+    const int total_rows = n_tokens * n_heads;
 #define GTG_LATENT(NT)                                                                                              \
     do {                                                                                                            \
         static bool configured = false;                                                                             \
@@ -337,13 +424,15 @@ GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo
             if (e != cudaSuccess) return (int)e;                                                                    \
             configured = true;                                                                                      \
         }                                                                                                           \
-        return launch_chained(latent_attention_mma_kernel<NT>, grid, dim3(kLatThreads), smem, stream, (const bf16*)q, ldq, \
-                              (bf16*)out, ldo, (const bf16*)kc, page_stride, block_table, table_stride, cu_seqlens, slots, \
-                              start_pos, n_heads, D, rank, scale, window);                                          \
+        st = launch_chained(latent_attention_mma_kernel<NT>, grid, dim3(kLatThreads), smem, stream, (const bf16*)q, ldq, \
+                            (bf16*)out, ldo, (const bf16*)kc, page_stride, block_table, table_stride, cu_seqlens, slots, \
+                            start_pos, n_heads, D, rank, scale, window, n_splits, scratch, total_rows);             \
     } while (0)
     const int per = ((rank / 8) + 3) / 4;
-    if (per <= 4) GTG_LATENT(4);
-    if (per <= 8) GTG_LATENT(8);
-    GTG_LATENT(16);
+    int st = 0;
+    if (per <= 4) GTG_LATENT(4); else if (per <= 8) GTG_LATENT(8); else GTG_LATENT(16);
 #undef GTG_LATENT
+    if (st != 0 || n_splits == 1) return st;
+    return launch_chained(latent_attention_merge_kernel, dim3(total_rows), dim3(128), 0, stream, (const float*)scratch,
+                          (bf16*)out, ldo, n_heads, rank, n_splits, total_rows);
 }

@@ -67,7 +67,10 @@ _SIGNATURES = {
     "gtg_latent_prepare": ("latent", [_I, _P, _I, _P, _I, _P, _P, _F, _P, _L, _P, _I, _P, _P, _P, _P, _I,
                                       _I, _I, _I, _I, _I, _I, _P]),
     "gtg_latent_attention_supports": ("latent", [_I, _I]),
-    "gtg_latent_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
+    "gtg_latent_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _I, _P]),
+    "gtg_latent_attention_splits": ("latent", [_I, _I, _I, _I, _I, _I]),
+    "gtg_moe_gather": ("experts", [_P, _I, _P, _I, _P, _I, _I, _P]),
+    "gtg_gemm_bf16_tcgen05_grouped": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
     "gtg_moe_route": ("experts", [_I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "gtg_moe_arrange": ("experts", [_P, _I, _I, _I, _I, _P, _P, _P, _P]),
     "gtg_moe_product_simt": ("experts", [_I, _I, _P, _I, _P, _I, _P, _I, _L, _P, _I, _P, _I, _I, _I, _P]),
@@ -980,13 +983,28 @@ def latent_attention_supports(kv, rank: int) -> bool:
             and bool(_fn("gtg_latent_attention_supports")(kv.head_dim, int(rank))))
 
 
+def latent_attention_plan(n_seqs: int, max_q_len: int, n_heads: int, head_dim: int, rank: int, max_kv_len: int,
+                          window: int = 0):
+    """(n_splits, scratch floats per token) for `latent_attention_bf16`: into how many
+    runs the keys of a block of query rows are cut so that a step with few rows
+    (a decode step) still fills the device; 1 for prompts.  It depends on the
+    step's sizes only, never on the data."""
+    splits = int(_fn("gtg_latent_attention_splits")(n_seqs, max_q_len, n_heads, head_dim, int(max_kv_len), int(window)))
+    if rank % 2:
+        splits = 1
+    return splits, (splits * n_heads * (rank + 2) if splits > 1 else 0)
+
+
 def latent_attention_bf16(q: torch.Tensor, out: torch.Tensor, kv, cu_seqlens, slots, start_pos, n_seqs: int,
-                          max_q_len: int, n_heads: int, rank: int, scale: float, window: int = 0) -> None:
+                          max_q_len: int, n_heads: int, rank: int, scale: float, window: int = 0,
+                          n_splits: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
     """Attention of every (token, head) of the step over its sequence's cache rows
     (one shared head of kv.head_dim channels, the first `rank` of which are the
     values): q [N, heads * head_dim] folded query rows, out [N, heads * rank].
     Causal, over the last `window` keys (0: all).  Prompts, portions and single
-    tokens alike."""
+    tokens alike.  With n_splits > 1 (`latent_attention_plan`) the keys are cut into
+    runs whose results a second kernel merges; `scratch` then holds N times the
+    plan's floats per token."""
     _rows2d(q, "latent_attention: q"); _rows2d(out, "latent_attention: out")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and latent_attention_supports(kv, rank),
           "latent_attention_bf16: bfloat16 rows of a multiple of 16 channels, a multiple of 8 of them values")
@@ -994,11 +1012,15 @@ def latent_attention_bf16(q: torch.Tensor, out: torch.Tensor, kv, cu_seqlens, sl
           and out.stride(0) % 2 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 4 == 0,
           "latent_attention_bf16: q [N, heads * head_dim] and out [N, heads * rank], aligned rows")
     _int32("latent_attention_bf16", cu_seqlens, slots, start_pos)
+    if n_splits > 1:
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
+              and scratch.numel() >= n_splits * q.shape[0] * n_heads * (rank + 2), "latent_attention_bf16: scratch is too small")
     _check_access("latent_attention_bf16", 2, kv, slots, start_pos=start_pos, cu_seqlens=cu_seqlens, n_items=n_seqs)
     _check(_fn("gtg_latent_attention_bf16")(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), kv.page_stride,
                                             _ptr(kv.block_table), kv.table_stride, _ptr(cu_seqlens), _ptr(slots), _ptr(start_pos),
                                             int(n_seqs), int(max_q_len), n_heads, kv.head_dim, int(rank), float(scale), int(window),
-                                            _stream()), "latent_attention_bf16")
+                                            int(n_splits), _ptr(scratch) if n_splits > 1 else None, q.shape[0], _stream()),
+           "latent_attention_bf16")
 
 
 # ------------------------------------------------------------------ routed experts
@@ -1039,6 +1061,17 @@ def moe_arrange(chosen: torch.Tensor, n_experts: int, row_item: torch.Tensor, it
                                   _stream()), "moe_arrange")
 
 
+def moe_gather(x: torch.Tensor, row_item: torch.Tensor, item_div: int, out: torch.Tensor) -> None:
+    """out[row, :] = x[row_item[row] // item_div, :], zeros for padding rows: the inputs of a
+    step's (token, expert) pairs in arranged order (bfloat16, a multiple of 8 channels)."""
+    _rows2d(x, "moe_gather: x")
+    _need(x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.is_contiguous()
+          and tuple(out.shape) == (row_item.numel(), x.shape[1]), "moe_gather: bfloat16 x [N, H] and out [rows, H]")
+    _int32("moe_gather", row_item)
+    _check(_fn("gtg_moe_gather")(_ptr(x), x.stride(0), _ptr(row_item), int(item_div), _ptr(out), out.shape[0], x.shape[1], _stream()),
+           "moe_gather")
+
+
 def moe_product_fused_supports(a: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether `moe_product` runs these operands on the tensor cores (where it can
     apply the gated silu in its epilogue)."""
@@ -1049,8 +1082,9 @@ def moe_product(a: torch.Tensor, row_item: torch.Tensor, item_div: int, w: torch
                 out: torch.Tensor, epilogue: str = "none") -> None:
     """out[row, :] = a[source(row), :] . w[expert of the row's tile]^T over arranged
     rows.  item_div > 0: the source is the pair's token, row_item[row] // item_div
-    (a holds tokens); 0: the row itself (a holds arranged rows).  w [E, N, K].
-    The tile is out's rows over tile_expert's length: 64, or 128 on the tensor
+    (a holds tokens); 0: the row itself (a holds arranged rows, zeros in its padding
+    rows: `moe_gather`), which in tiles of 128 takes the prompt-sized tensor-memory
+    product.  w [E, N, K].  The tile is out's rows over tile_expert's length: 64, or 128 on the tensor
     cores.  epilogue="swiglu" (tensor cores only: `moe_product_fused_supports`):
     every w[e] is laid out by `interleave_gate_up` and out [rows, N/2] = silu(gate) * up."""
     _rows2d(a, "moe_product: a"); _rows2d(out, "moe_product: out")
@@ -1066,6 +1100,14 @@ def moe_product(a: torch.Tensor, row_item: torch.Tensor, item_div: int, w: torch
     if moe_product_fused_supports(a, w):
         _need(tile in (64, 128), f"moe_product: tiles of 64 or 128 rows, not {tile}")
         _need(epilogue == "none" or N % 16 == 0, "moe_product: the fused gated silu needs a multiple of 16 rows per expert")
+        if (tile == 128 and item_div == 0 and out.data_ptr() % 16 == 0
+                and out.stride(0) % (4 if out.dtype == torch.float32 else 8) == 0):
+            # arranged rows in tiles of 128: the prompt-sized product (tensor copies, tensor memory)
+            _check(_fn("gtg_gemm_bf16_tcgen05_grouped")(_ptr(a), a.stride(0), _ptr(w), K, _ptr(out), out.stride(0),
+                                                        1 if out.dtype == torch.float32 else 0, cap * tile, N, K,
+                                                        1 if epilogue == "swiglu" else 0, _ptr(tile_expert), E, _stream()),
+                   "moe_product(tcgen05)")
+            return
         _check(_fn("gtg_gemm_bf16_grouped")(_ptr(a), a.stride(0), 0, _ptr(row_item), int(item_div), _ptr(w), K, N * K,
                                             _ptr(tile_expert), _ptr(out), out.stride(0), 0, 1 if out.dtype == torch.float32 else 0,
                                             1, cap * tile, N, K, tile, 1 if epilogue == "swiglu" else 0, None, 0, 0, _stream()),

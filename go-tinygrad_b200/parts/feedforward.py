@@ -176,7 +176,12 @@ class RoutedExperts(FeedForward):
         tile_expert = rt.empty(tiles, dtype=torch.int32)
         ops.moe_arrange(chosen, E, row_item, item_row, tile_expert, tile)
         act = rt.empty(rows, self.inter)
-        if fused:
+        if fused and tile == 128:
+            # prompt-sized: the inputs copied into arranged order, for the product that tensor copies feed
+            gathered = rt.empty(rows, self.hidden)
+            ops.moe_gather(x, row_item, top, gathered)
+            ops.moe_product(gathered, row_item, 0, self.w_gate_up, tile_expert, act, epilogue="swiglu")
+        elif fused:
             ops.moe_product(x, row_item, top, self.w_gate_up, tile_expert, act, epilogue="swiglu")
         else:
             sums = rt.empty(rows, 2 * self.inter, dtype=torch.float32)

@@ -125,8 +125,11 @@ class LatentAttention(Mixer):
         ctx.trace("q_attn", folded)
         attended = rt.empty(n, H * self.rank)
         if rt.dtype == torch.bfloat16 and ops.latent_attention_supports(kv, self.rank):
+            splits, floats = ops.latent_attention_plan(ctx.n_seqs, ctx.max_q_len, H, self.row, self.rank, ctx.max_kv_len,
+                                                       self.window or 0)
+            scratch = rt.empty(n * floats, dtype=torch.float32) if splits > 1 else None
             ops.latent_attention_bf16(folded, attended, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, ctx.n_seqs,
-                                      ctx.max_q_len, H, self.rank, self.scale, self.window or 0)
+                                      ctx.max_q_len, H, self.rank, self.scale, self.window or 0, splits, scratch)
         else:
             # float32, and row sizes the tensor-core kernel does not take
             ops.attention_simple(folded, attended, kv, ctx.token_seq, ctx.slots, ctx.positions, H, self.scale,

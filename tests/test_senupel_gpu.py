@@ -282,16 +282,23 @@ def test_tensor_core_attention_over_latent_rows(heads, row, rank, window):
     out = torch.zeros(sum(new), heads * rank, dtype=torch.bfloat16, device=DEV)
     scale = 1.7 / np.sqrt(row)
     ops.latent_attention_bf16(q, out, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, len(new), max(new), heads, rank, scale, window)
-    got, q64, at = f64(out).reshape(-1, heads, rank), f64(q).reshape(-1, heads, row), 0
-    for r, a, n in zip(rows, starts, new):
-        for i in range(n):
-            pos = a + i
-            lo = max(0, pos - window + 1) if window else 0
-            sc = q64[at + i] @ r[lo:pos + 1].T * scale
-            w = np.exp(sc - sc.max(-1, keepdims=True))
-            want = (w / w.sum(-1, keepdims=True)) @ r[lo:pos + 1, :rank]
-            assert np.abs(got[at + i] - want).max() <= 2e-2 * max(1.0, np.abs(want).max()), (a, i, np.abs(got[at + i] - want).max())
-        at += n
+    # the same with every block's keys cut into three runs (one of them often empty) and merged
+    cut = torch.zeros_like(out)
+    scratch = torch.empty(3 * sum(new) * heads * (rank + 2), dtype=torch.float32, device=DEV)
+    ops.latent_attention_bf16(q, cut, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos, len(new), max(new), heads, rank, scale, window,
+                              n_splits=3, scratch=scratch)
+    q64 = f64(q).reshape(-1, heads, row)
+    for result in (out, cut):
+        got, at = f64(result).reshape(-1, heads, rank), 0
+        for r, a, n in zip(rows, starts, new):
+            for i in range(n):
+                pos = a + i
+                lo = max(0, pos - window + 1) if window else 0
+                sc = q64[at + i] @ r[lo:pos + 1].T * scale
+                w = np.exp(sc - sc.max(-1, keepdims=True))
+                want = (w / w.sum(-1, keepdims=True)) @ r[lo:pos + 1, :rank]
+                assert np.abs(got[at + i] - want).max() <= 2e-2 * max(1.0, np.abs(want).max()), (a, i, np.abs(got[at + i] - want).max())
+            at += n
 
 
 def _latent_mixer(dtype, m, hidden, weights, own_kv=True):
@@ -432,13 +439,15 @@ def test_gated_feed_forward_with_biases(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("experts,top", [(5, 1), (3, 3), (12, 4), (40, 2)])
-def test_routed_experts_choose_weigh_and_add_up(dtype, experts, top):
+@pytest.mark.parametrize("experts,top,hidden,ff,n", [(5, 1, 48, 20, 150), (3, 3, 48, 24, 150), (12, 4, 48, 20, 150),
+                                                     (40, 2, 40, 12, 150), (4, 2, 128, 64, 600)])
+def test_routed_experts_choose_weigh_and_add_up(dtype, experts, top, hidden, ff, n):
     """Router weights large enough that no choice is a close call; the chosen set,
     its weights and the sum are the plain implementation's, whatever else is in
-    the batch and however few tokens there are."""
+    the batch and however few tokens there are.  Few tokens an expert take the
+    products over tiles of 64 rows, many (the second and the last case) the
+    prompt-sized product over tiles of 128; sizes that are no multiple of 8 the plain one."""
     rng = np.random.default_rng(experts * 10 + top)
-    hidden, ff, n = 48, 20, 150
     w = {"router": (t32(rng.standard_normal((experts, hidden)))).to(torch.bfloat16),
          "router.b": t32(rng.standard_normal(experts)).to(torch.bfloat16)}
     for e in range(experts):
