@@ -649,7 +649,10 @@ def run_design(args):
             add(f"linear, as many FLOPs ({tag})", n, timed(lambda: ops.linear(xl, wl, ol)), wl.numel() * 2 + n * (heads * dim + rank) * 2, fl, like="linear_heads")
             # attention
             keys = (ctx_len + per) * n_seqs if per == 1 else sum(min(i + 1, window) for i in range(per))
-            add(f"latent_attention ({tag})", n, timed(lambda: ops.latent_attention_bf16(folded, att, kv, cu, slots, start, n_seqs, per, heads, rank, 0.07, window)),
+            splits, floats = ops.latent_attention_plan(n_seqs, per, heads, row, rank, ctx_len + per, window)
+            runs = torch.empty(max(1, n * floats), dtype=f32, device=dev)
+            add(f"latent_attention, keys in {splits} run(s) ({tag})", n,
+                timed(lambda: ops.latent_attention_bf16(folded, att, kv, cu, slots, start, n_seqs, per, heads, rank, 0.07, window, splits, runs)),
                 n * heads * (row + rank) * 2 + (n_seqs * (ctx_len + per)) * row * 2, 2 * heads * keys * (row + rank))
             ql, ml = rnd(n, heads * 128), torch.empty(n, heads * 128, dtype=bf, device=dev)
             if per == 1:
@@ -679,8 +682,15 @@ def run_design(args):
             wgu, wd = rnd(E, 2 * eff, H), rnd(E, H, eff)
             acts, y = torch.empty(tiles * tile, eff, dtype=bf, device=dev), torch.empty(tiles * tile, H, dtype=f32, device=dev)
             used = min(E, n * top)
-            add(f"moe_product gate, up, silu ({tag})", n, timed(lambda: ops.moe_product(x, row_item, top, wgu, tile_expert, acts, epilogue="swiglu")),
-                used * 2 * eff * H * 2 + n * H * 2 + n * top * eff * 2, 2 * n * top * 2 * eff * H)
+            if tile == 128:
+                # as the part does for prompts: the inputs copied into arranged order, then the product over them
+                gathered = torch.empty(tiles * tile, H, dtype=bf, device=dev)
+                add(f"moe_gather ({tag})", n, timed(lambda: ops.moe_gather(x, row_item, top, gathered)), n * H * 2 + n * top * H * 2)
+                add(f"moe_product gate, up, silu ({tag})", n, timed(lambda: ops.moe_product(gathered, row_item, 0, wgu, tile_expert, acts, epilogue="swiglu")),
+                    used * 2 * eff * H * 2 + n * top * (H + eff) * 2, 2 * n * top * 2 * eff * H)
+            else:
+                add(f"moe_product gate, up, silu ({tag})", n, timed(lambda: ops.moe_product(x, row_item, top, wgu, tile_expert, acts, epilogue="swiglu")),
+                    used * 2 * eff * H * 2 + n * H * 2 + n * top * eff * 2, 2 * n * top * 2 * eff * H)
             add(f"moe_product down ({tag})", n, timed(lambda: ops.moe_product(acts, row_item, 0, wd, tile_expert, y)),
                 used * eff * H * 2 + n * top * (eff * 2 + H * 4), 2 * n * top * eff * H)
             wg2, a2 = rnd(2 * eff * top, H), torch.empty(n, eff * top, dtype=bf, device=dev)

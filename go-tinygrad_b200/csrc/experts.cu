@@ -45,10 +45,21 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
         const float* r0 = router + (size_t)e * H;
         const float* r1 = router + (size_t)(two ? e + 1 : e) * H;
         float s0 = 0.f, s1 = 0.f;
-        for (int i = lane; i < H; i += 32) {
-            const float v = xs[i];
-            s0 = fmaf(v, r0[i], s0);
-            s1 = fmaf(v, r1[i], s1);
+        if (H % 128 == 0 && (reinterpret_cast<uintptr_t>(router) % 16) == 0) {
+            // four channels a lane and step, the loads of several steps in flight together
+#pragma unroll 4
+            for (int i = lane * 4; i < H; i += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(xs + i);
+                const float4 a = *reinterpret_cast<const float4*>(r0 + i), b = *reinterpret_cast<const float4*>(r1 + i);
+                s0 = fmaf(v.x, a.x, s0); s0 = fmaf(v.y, a.y, s0); s0 = fmaf(v.z, a.z, s0); s0 = fmaf(v.w, a.w, s0);
+                s1 = fmaf(v.x, b.x, s1); s1 = fmaf(v.y, b.y, s1); s1 = fmaf(v.z, b.z, s1); s1 = fmaf(v.w, b.w, s1);
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) {
+                const float v = xs[i];
+                s0 = fmaf(v, r0[i], s0);
+                s1 = fmaf(v, r1[i], s1);
+            }
         }
         s0 = warp_sum(s0);
         s1 = warp_sum(s1);
@@ -59,25 +70,25 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
     }
     __syncthreads();
     if (threadIdx.x == 0) {
+        // top <= E rounds of a first-maximum search; a chosen logit becomes NaN, which no comparison picks again
         float best0 = 0.f, total = 0.f;
         for (int k = 0; k < top; ++k) {
             int arg = -1;
             float best = -INFINITY;
             for (int e = 0; e < E; ++e) {
-                bool taken = false;
-                for (int j = 0; j < k; ++j) taken |= chosen[(size_t)n * top + j] == e;
-                if (taken) continue;
                 const float v = z[e];
+                if (v != v) continue;                       // chosen in an earlier round
                 if (arg < 0 || v > best) { best = v; arg = e; }
             }
+            z[arg] = __int_as_float(0x7fc00000);
             if (k == 0) best0 = best;
             chosen[(size_t)n * top + k] = arg;
             const float p = expf(best - best0);
-            weights[(size_t)n * top + k] = p;
+            xs[k] = p;                                      // the staged row is no longer needed (top <= E <= H is checked)
             total += p;
         }
         const float inv = 1.0f / total;
-        for (int k = 0; k < top; ++k) weights[(size_t)n * top + k] *= inv;
+        for (int k = 0; k < top; ++k) weights[(size_t)n * top + k] = xs[k] * inv;
     }
 }
 
@@ -213,6 +224,7 @@ GTG_API int gtg_moe_route(int dtype, const void* x, int ldx, const float* router
                           float* weights, int N, int H, int E, int top, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || H <= 0) return kErrBadArgument;
+    if (top > H) return kErrUnsupported;
     const size_t smem = (size_t)(H + E) * sizeof(float);
     if (smem > 48 * 1024) return kErrUnsupported;
     const dim3 grid(N);

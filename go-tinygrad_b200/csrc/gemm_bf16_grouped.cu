@@ -25,6 +25,15 @@ template <typename OutT>
 __device__ __forceinline__ void put(OutT* p, float v);
 template <> __device__ __forceinline__ void put<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ void put<float>(float* p, float v) { *p = v; }
+// two neighbouring columns at once (the address is a multiple of two elements)
+template <typename OutT>
+__device__ __forceinline__ void put2(OutT* p, float v0, float v1);
+template <> __device__ __forceinline__ void put2<bf16>(bf16* p, float v0, float v1) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v0, v1);
+}
+template <> __device__ __forceinline__ void put2<float>(float* p, float v0, float v1) {
+    *reinterpret_cast<float2*>(p) = make_float2(v0, v1);
+}
 
 template <int BM, typename OutT>
 __global__ void __launch_bounds__(kThreads)
@@ -137,6 +146,9 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const
     cp_async_wait<0>();
 
     const int g = lane >> 2, t = lane & 3;
+    // pairs of columns go out in one access where every pair's address is aligned
+    const bool pairs = (ldc % 2 == 0) && (batch_c % 2 == 0) && ((reinterpret_cast<uintptr_t>(C) % (2 * sizeof(OutT))) == 0) &&
+                       (epilogue != 2 || ((ldg % 2 == 0) && (batch_g % 2 == 0) && (reinterpret_cast<uintptr_t>(G) % 4) == 0));
 #pragma unroll
     for (int i = 0; i < MI; ++i) {
 #pragma unroll
@@ -148,6 +160,12 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const
 #pragma unroll
                 for (int j = 0; j < 4; j += 2) {
                     const int n = n0 + wn * 32 + j * 8;              // a block of 8 gate rows, then their 8 up rows
+                    if (pairs && n + 16 <= N) {
+                        const float g0 = acc[i][j][half * 2], g1 = acc[i][j][half * 2 + 1];
+                        put2<OutT>(C + m * ldc + n / 2 + t * 2, g0 / (1.0f + expf(-g0)) * acc[i][j + 1][half * 2],
+                                   g1 / (1.0f + expf(-g1)) * acc[i][j + 1][half * 2 + 1]);
+                        continue;
+                    }
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int col = n / 2 + t * 2 + e;
@@ -160,6 +178,17 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, long long batch_a, const
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
+                    const int n2 = n0 + wn * 32 + j * 8 + t * 2;
+                    if (pairs && n2 + 1 < N) {
+                        float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
+                        if (epilogue == 2) {
+                            const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(G + m * ldg + n2));
+                            v0 *= 1.0f / (1.0f + expf(-gg.x));
+                            v1 *= 1.0f / (1.0f + expf(-gg.y));
+                        }
+                        put2<OutT>(C + m * ldc + n2, v0, v1);
+                        continue;
+                    }
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int n = n0 + wn * 32 + j * 8 + t * 2 + e;

@@ -167,21 +167,21 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
         row_pos[tid] = r < n_new * n_heads ? start + r / n_heads : -1;
     }
     const int chunks = D / 8;
-    for (int id = tid; id < kTileRows * chunks; id += kLatThreads) {
-        const int r = id / chunks, c = id % chunks;
+    for (int r = warp; r < kTileRows; r += kLatThreads / 32) {
         const int row = r0 + r;
         const bool ok = row < n_new * n_heads;
-        const bf16* src = ok ? q + (size_t)(tok0 + row / n_heads) * ldq + (size_t)(row % n_heads) * D + c * 8 : q;
-        cp_async16(smem_u32(q_s + r * ldr + c * 8), src, ok ? 16 : 0);
+        const bf16* src = ok ? q + (size_t)(tok0 + row / n_heads) * ldq + (size_t)(row % n_heads) * D : q;
+        for (int c = lane; c < chunks; c += 32)
+            cp_async16(smem_u32(q_s + r * ldr + c * 8), ok ? src + c * 8 : q, ok ? 16 : 0);
     }
 
     auto load_page = [&](int buf, int p) {
+        // a warp takes every eighth row, a lane every 32nd chunk of 16 bytes: no division per copy
         const bf16* src = kc + (size_t)table[p] * page_stride;
         bf16* dst = page_s + (size_t)buf * kPageTokens * ldr;
-        for (int id = tid; id < kPageTokens * chunks; id += kLatThreads) {
-            const int r = id / chunks, c = id % chunks;
-            cp_async16(smem_u32(dst + r * ldr + c * 8), src + (size_t)r * D + c * 8, 16);
-        }
+        for (int r = warp; r < kPageTokens; r += kLatThreads / 32)
+            for (int c = lane; c < chunks; c += 32)
+                cp_async16(smem_u32(dst + r * ldr + c * 8), src + (size_t)r * D + c * 8, 16);
     };
     load_page(0, page_lo);
     cp_async_commit();
@@ -196,6 +196,9 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    // a row group without a live row (a decode step of at most 16 heads fills one group of two)
+    // multiplies nothing; it still stages pages and meets the barriers
+    const bool rg_live = r0 + rg * 16 <= last_row;
     __syncthreads();                                            // row_pos
     int pos_r[2], lo_r[2];
 #pragma unroll
@@ -218,16 +221,41 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
         for (int j = 0; j < 2; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
-        {
+        if (rg_live) {
+            // fragments of channel step k+1 are asked for before the products of step k are issued, and
+            // even and odd steps add into accumulators of their own: two chains instead of one
             const uint32_t a_addr = smem_u32(q_s + (rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldr + (lane >> 4) * 8);
             const uint32_t b_addr = smem_u32(pg + (quarter * 16 + (lane & 7) + (lane >> 4) * 8) * ldr + ((lane >> 3) & 1) * 8);
-            for (int ks = 0; ks < D / 16; ++ks) {
-                uint32_t a[4], b0, b1, b2, b3;
-                ldmatrix_x4(a[0], a[1], a[2], a[3], a_addr + ks * 32);
-                ldmatrix_x4(b0, b1, b2, b3, b_addr + ks * 32);
-                mma_bf16_16816(s[0], a, b0, b1);
-                mma_bf16_16816(s[1], a, b2, b3);
+            const int n_ks = D / 16;
+            float s2[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s2[j][e] = 0.f;
+            uint32_t a0[4], b0[4], a1[4], b1[4];
+            ldmatrix_x4(a0[0], a0[1], a0[2], a0[3], a_addr);
+            ldmatrix_x4(b0[0], b0[1], b0[2], b0[3], b_addr);
+            int ks = 0;
+            for (; ks + 2 <= n_ks; ks += 2) {
+                ldmatrix_x4(a1[0], a1[1], a1[2], a1[3], a_addr + (ks + 1) * 32);
+                ldmatrix_x4(b1[0], b1[1], b1[2], b1[3], b_addr + (ks + 1) * 32);
+                mma_bf16_16816(s[0], a0, b0[0], b0[1]);
+                mma_bf16_16816(s[1], a0, b0[2], b0[3]);
+                if (ks + 2 < n_ks) {
+                    ldmatrix_x4(a0[0], a0[1], a0[2], a0[3], a_addr + (ks + 2) * 32);
+                    ldmatrix_x4(b0[0], b0[1], b0[2], b0[3], b_addr + (ks + 2) * 32);
+                }
+                mma_bf16_16816(s2[0], a1, b1[0], b1[1]);
+                mma_bf16_16816(s2[1], a1, b1[2], b1[3]);
             }
+            if (ks < n_ks) {
+                mma_bf16_16816(s[0], a0, b0[0], b0[1]);
+                mma_bf16_16816(s[1], a0, b0[2], b0[3]);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] += s2[j][e];
         }
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -288,21 +316,28 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
             o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
         }
         // O += P . page[:, my value channels]
-        {
+        if (rg_live) {
+            // per 16 keys: the value fragments of up to eight channel tiles are asked for together, then multiplied
             const uint32_t a_addr = smem_u32(p_s + (rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * (kPageTokens + kPad) + (lane >> 4) * 8);
             const uint32_t v_addr = smem_u32(pg + ((lane & 7) + ((lane >> 3) & 1) * 8) * ldr + tile_lo * 8 + (lane >> 4) * 8);
+            constexpr int CH = NT < 8 ? NT : 8;
 #pragma unroll
             for (int ks = 0; ks < kPageTokens / 16; ++ks) {
                 uint32_t a[4];
                 ldmatrix_x4(a[0], a[1], a[2], a[3], a_addr + ks * 32);
 #pragma unroll
-                for (int j = 0; j < NT; j += 2) {
-                    if (j < my_tiles) {
-                        uint32_t b0, b1, b2, b3;
-                        ldmatrix_x4_trans(b0, b1, b2, b3, v_addr + (ks * 16 * ldr + j * 8) * 2);
-                        mma_bf16_16816(o[j], a, b0, b1);
-                        if (j + 1 < NT) mma_bf16_16816(o[j + 1], a, b2, b3);
-                    }
+                for (int c = 0; c < NT; c += CH) {
+                    uint32_t v[CH / 2][4];
+#pragma unroll
+                    for (int j = 0; j < CH; j += 2)
+                        if (c + j < my_tiles)
+                            ldmatrix_x4_trans(v[j / 2][0], v[j / 2][1], v[j / 2][2], v[j / 2][3], v_addr + (ks * 16 * ldr + (c + j) * 8) * 2);
+#pragma unroll
+                    for (int j = 0; j < CH; j += 2)
+                        if (c + j < my_tiles) {
+                            mma_bf16_16816(o[c + j], a, v[j / 2][0], v[j / 2][1]);
+                            mma_bf16_16816(o[c + j + 1], a, v[j / 2][2], v[j / 2][3]);
+                        }
                 }
             }
         }
@@ -341,25 +376,29 @@ latent_attention_merge_kernel(const float* __restrict__ scratch, bf16* __restric
                               int n_splits, int total_rows) {
     chain_release();
     chain_wait();
+    __shared__ float ms[64], ls[64], ws[64];
     const int row = blockIdx.x;
     const size_t stride = (size_t)total_rows * (rank + 2);
     const float* base = scratch + (size_t)row * (rank + 2);
-    float M = -INFINITY;
-    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, base[z * stride]);
-    if (M == -INFINITY) return;
-    float L = 0.f;
-    for (int z = 0; z < n_splits; ++z) {
-        const float m = base[z * stride];
-        if (m != -INFINITY) L += expf(m - M) * base[z * stride + 1];
+    if (threadIdx.x < n_splits) {
+        ms[threadIdx.x] = base[threadIdx.x * stride];
+        ls[threadIdx.x] = base[threadIdx.x * stride + 1];
     }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, ms[z]);
+    if (M == -INFINITY) return;
+    if (threadIdx.x < n_splits) ws[threadIdx.x] = ms[threadIdx.x] == -INFINITY ? 0.f : expf(ms[threadIdx.x] - M);
+    __syncthreads();
+    float L = 0.f;
+    for (int z = 0; z < n_splits; ++z) L = fmaf(ws[z], ls[z], L);
     const float inv = 1.0f / L;
     bf16* dst = out + (size_t)(row / n_heads) * ldo + (size_t)(row % n_heads) * rank;
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
         float acc = 0.f;
-        for (int z = 0; z < n_splits; ++z) {
-            const float m = base[z * stride];
-            if (m != -INFINITY) acc = fmaf(expf(m - M), base[z * stride + 2 + c], acc);
-        }
+#pragma unroll 4
+        for (int z = 0; z < n_splits; ++z)
+            if (ws[z] != 0.f) acc = fmaf(ws[z], base[z * stride + 2 + c], acc);
         dst[c] = __float2bfloat16_rn(acc * inv);
     }
 }
