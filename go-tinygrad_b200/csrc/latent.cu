@@ -102,23 +102,57 @@ GTG_API int gtg_latent_prepare(int dtype, const void* q, int ldq, const void* dk
 // sequence's new tokens are one list of query rows; a thread block takes 32
 // consecutive ones (two tokens of 16 heads, a quarter of a token of 128, eleven
 // of 3) and walks the pages their windows span, each page staged once in shared
-// memory by cp.async, two pages in flight.  Per page, eight warps as 2 row
-// groups x 4: first every warp multiplies its 16 query rows with a quarter of
+// memory by the copy engine (a bulk copy a row, counted on the page's barrier; waits
+// are bounded), two pages in flight.  Per page, sixteen warps as 2 row
+// groups x 8: first every warp multiplies its 16 query rows with an eighth of
 // the page's 64 keys over all rank + rot channels (S, float), the row maxima and
 // sums meet through shared memory (streaming softmax in float, expf), the
 // weights go to shared memory as bfloat16; then every warp adds, for its 16
-// rows, a quarter of the value channels: O[16, rank/4] += P[16, 64] . page[64,
-// quarter], the page's first rank columns read transposed (ldmatrix.trans).  O
-// stays in registers (up to 64 floats a thread at rank 512).  Prompts, portions
+// rows, an eighth of the value channels: O[16, rank/8] += P[16, 64] . page[64,
+// eighth], the page's first rank columns read transposed (ldmatrix.trans).  O
+// stays in registers (up to 32 floats a thread at rank 512).  Sixteen warps, not
+// eight, because a block has a multiprocessor to itself (its staged pages fill the
+// shared memory) and two warps a scheduler hid too little latency.  Prompts, portions
 // and single tokens are one code path; a row sees keys lo..pos of its sequence,
 // lo = 0 or pos - window + 1.  Needs rank + rot a multiple of 16 and rank of 8.
 
+// 0, or 1 if a block ever gave up waiting for a page it had asked for (it then went on with
+// whatever the buffer held: the result of that launch is not to be used).
+__device__ int g_latent_status = 0;
+
 namespace {
+constexpr unsigned kPageWaitLimit = 1u << 22;      // polls of a page's barrier before a block gives up
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Polls until the phase with `parity` completes or the limit is hit (then the status word is set).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (unsigned i = 0; i < kPageWaitLimit; ++i) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                     "selp.u32 %0, 1, 0, p;\n}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    atomicExch(&g_latent_status, 1);
+    return false;
+}
+// One row of `bytes` (a multiple of 16, both addresses 16-byte aligned) global -> shared by the copy
+// engine; its arrival is counted on the barrier.
+__device__ __forceinline__ void bulk_row(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
 constexpr int kTileRows = 32;
-constexpr int kLatThreads = 256;
+constexpr int kLatThreads = 512;
+constexpr int kParts = 8;            // warps that share a row group: each takes 8 of a page's 64 keys, then an eighth of the value channels
 constexpr int kPad = 8;              // bfloat16 of padding per staged row: rows fall into different banks
 
-template <int NT>                    // value n-tiles (8 channels) per warp at most: rank <= 32 * NT
+template <int NT>                    // value n-tiles (8 channels) per warp at most: rank <= 64 * NT
 __global__ void __launch_bounds__(kLatThreads)
 latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
                             const bf16* __restrict__ kc, long long page_stride, const int* __restrict__ block_table,
@@ -133,14 +167,15 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
     const int r0 = blockIdx.x * kTileRows;
     if (r0 >= n_new * n_heads) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int rg = warp & 1, quarter = warp >> 1;
+    const int rg = warp & 1, part_i = warp >> 1;
     const int g = lane >> 2, t = lane & 3;
     const int ldr = D + kPad;                                   // staged row, in elements
     bf16* q_s = reinterpret_cast<bf16*>(smem);                  // [32][ldr]
     bf16* page_s = q_s + kTileRows * ldr;                       // [2][64][ldr]
     bf16* p_s = page_s + 2 * kPageTokens * ldr;                 // [32][64 + kPad]
-    float* part = reinterpret_cast<float*>(p_s + kTileRows * (kPageTokens + kPad));   // [2][4][32]: maxima, sums
-    int* row_pos = reinterpret_cast<int*>(part + 2 * 4 * kTileRows);                  // [32] position or -1
+    float* part = reinterpret_cast<float*>(p_s + kTileRows * (kPageTokens + kPad));   // [2][8][32]: maxima, sums
+    int* row_pos = reinterpret_cast<int*>(part + 2 * kParts * kTileRows);                  // [32] position or -1
+    const uint32_t bars = smem_u32(row_pos + kTileRows);        // two barriers of 8 bytes: a staged page has arrived
     const int start = start_pos[b];
     const int* table = block_table + (size_t)slots[b] * table_stride;
     const int last_row = min(r0 + kTileRows, n_new * n_heads) - 1;
@@ -175,20 +210,30 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
             cp_async16(smem_u32(q_s + r * ldr + c * 8), ok ? src + c * 8 : q, ok ? 16 : 0);
     }
 
+    // A page is staged by the copy engine, a row a copy (64 copies, two a lane of warp 0), so that no
+    // warp that multiplies waits in a queue of copies; the page's barrier counts the bytes.
+    if (tid == 0) {
+        mbar_init(bars, 1);
+        mbar_init(bars + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
+    }
+    __syncthreads();                                            // barriers and row_pos
     auto load_page = [&](int buf, int p) {
-        // a warp takes every eighth row, a lane every 32nd chunk of 16 bytes: no division per copy
+        if (warp != 0) return;
         const bf16* src = kc + (size_t)table[p] * page_stride;
-        bf16* dst = page_s + (size_t)buf * kPageTokens * ldr;
-        for (int r = warp; r < kPageTokens; r += kLatThreads / 32)
-            for (int c = lane; c < chunks; c += 32)
-                cp_async16(smem_u32(dst + r * ldr + c * 8), src + (size_t)r * D + c * 8, 16);
+        const uint32_t dst = smem_u32(page_s + (size_t)buf * kPageTokens * ldr);
+        if (lane == 0) mbar_expect_tx(bars + 8 * buf, (uint32_t)(kPageTokens * D * 2));
+        __syncwarp();
+        for (int r = lane; r < kPageTokens; r += 32)
+            bulk_row(dst + (uint32_t)(r * ldr * 2), src + (size_t)r * D, (uint32_t)(D * 2), bars + 8 * buf);
     };
+    const int n_pages = page_hi - page_lo + 1;
     load_page(0, page_lo);
-    cp_async_commit();
+    cp_async_commit();                                          // the query rows
 
     const int tiles_total = rank / 8;
-    const int per = (tiles_total + 3) / 4;
-    const int tile_lo = quarter * per;
+    const int per = (tiles_total + kParts - 1) / kParts;
+    const int tile_lo = part_i * per;
     const int my_tiles = max(0, min(per, tiles_total - tile_lo));
     float o[NT][4];
 #pragma unroll
@@ -196,10 +241,10 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    cp_async_wait<0>();                                         // this thread's share of the query rows
     // a row group without a live row (a decode step of at most 16 heads fills one group of two)
     // multiplies nothing; it still stages pages and meets the barriers
     const bool rg_live = r0 + rg * 16 <= last_row;
-    __syncthreads();                                            // row_pos
     int pos_r[2], lo_r[2];
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
@@ -207,100 +252,75 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
         lo_r[hh] = (window > 0 && pos_r[hh] - window + 1 > 0) ? pos_r[hh] - window + 1 : 0;
     }
 
-    for (int p = page_lo; p <= page_hi; ++p) {
-        const int buf = (p - page_lo) & 1;
-        if (p > page_lo) __syncthreads();                       // everyone is done with the page before and its weights
-        if (p + 1 <= page_hi) load_page(buf ^ 1, p + 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();                                        // page p (and q) staged
+    for (int i = 0; i < n_pages; ++i) {
+        const int p = page_lo + i;
+        const int buf = i & 1;
+        if (i > 0) __syncthreads();                             // everyone is done with the page before and its weights
+        if (i + 1 < n_pages) load_page(buf ^ 1, p + 1);
+        mbar_wait(bars + 8 * buf, ((uint32_t)i >> 1) & 1u);     // page p has arrived
+        if (i == 0) __syncthreads();                            // and everyone's share of the query rows
         const bf16* pg = page_s + (size_t)buf * kPageTokens * ldr;
-        // S: rows rg*16.., keys quarter*16.. of the page
-        float s[2][4];
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+        // S: rows rg*16.., keys part_i*8.. of the page
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
         if (rg_live) {
-            // fragments of channel step k+1 are asked for before the products of step k are issued, and
+            // fragments of channel step k+1 are asked for before the product of step k is issued, and
             // even and odd steps add into accumulators of their own: two chains instead of one
             const uint32_t a_addr = smem_u32(q_s + (rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldr + (lane >> 4) * 8);
-            const uint32_t b_addr = smem_u32(pg + (quarter * 16 + (lane & 7) + (lane >> 4) * 8) * ldr + ((lane >> 3) & 1) * 8);
+            const uint32_t b_addr = smem_u32(pg + (part_i * 8 + (lane & 7)) * ldr + ((lane >> 3) & 1) * 8);
             const int n_ks = D / 16;
-            float s2[2][4];
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) s2[j][e] = 0.f;
-            uint32_t a0[4], b0[4], a1[4], b1[4];
+            float s2[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t a0[4], b0[2], a1[4], b1[2];
             ldmatrix_x4(a0[0], a0[1], a0[2], a0[3], a_addr);
-            ldmatrix_x4(b0[0], b0[1], b0[2], b0[3], b_addr);
+            ldmatrix_x2(b0[0], b0[1], b_addr);
             int ks = 0;
             for (; ks + 2 <= n_ks; ks += 2) {
                 ldmatrix_x4(a1[0], a1[1], a1[2], a1[3], a_addr + (ks + 1) * 32);
-                ldmatrix_x4(b1[0], b1[1], b1[2], b1[3], b_addr + (ks + 1) * 32);
-                mma_bf16_16816(s[0], a0, b0[0], b0[1]);
-                mma_bf16_16816(s[1], a0, b0[2], b0[3]);
+                ldmatrix_x2(b1[0], b1[1], b_addr + (ks + 1) * 32);
+                mma_bf16_16816(s, a0, b0[0], b0[1]);
                 if (ks + 2 < n_ks) {
                     ldmatrix_x4(a0[0], a0[1], a0[2], a0[3], a_addr + (ks + 2) * 32);
-                    ldmatrix_x4(b0[0], b0[1], b0[2], b0[3], b_addr + (ks + 2) * 32);
+                    ldmatrix_x2(b0[0], b0[1], b_addr + (ks + 2) * 32);
                 }
-                mma_bf16_16816(s2[0], a1, b1[0], b1[1]);
-                mma_bf16_16816(s2[1], a1, b1[2], b1[3]);
+                mma_bf16_16816(s2, a1, b1[0], b1[1]);
             }
-            if (ks < n_ks) {
-                mma_bf16_16816(s[0], a0, b0[0], b0[1]);
-                mma_bf16_16816(s[1], a0, b0[2], b0[3]);
-            }
+            if (ks < n_ks) mma_bf16_16816(s, a0, b0[0], b0[1]);
 #pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) s[j][e] += s2[j][e];
+            for (int e = 0; e < 4; ++e) s[e] += s2[e];
         }
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int hh = e >> 1;
-                const int key = p * kPageTokens + quarter * 16 + j * 8 + t * 2 + (e & 1);
-                const bool seen = pos_r[hh] >= 0 && key <= pos_r[hh] && key >= lo_r[hh];
-                s[j][e] = seen ? s[j][e] * scale : -INFINITY;
-                mx[hh] = fmaxf(mx[hh], s[j][e]);
-            }
+        for (int e = 0; e < 4; ++e) {
+            const int hh = e >> 1;
+            const int key = p * kPageTokens + part_i * 8 + t * 2 + (e & 1);
+            const bool seen = pos_r[hh] >= 0 && key <= pos_r[hh] && key >= lo_r[hh];
+            s[e] = seen ? s[e] * scale : -INFINITY;
+            mx[hh] = fmaxf(mx[hh], s[e]);
+        }
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
             mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
             mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
-            if (t == 0) part[quarter * kTileRows + rg * 16 + g + hh * 8] = mx[hh];
+            if (t == 0) part[part_i * kTileRows + rg * 16 + g + hh * 8] = mx[hh];
         }
         __syncthreads();
-        float corr[2], sum[2] = {0.f, 0.f};
+        float corr[2], sum[2];
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
             const int r = rg * 16 + g + hh * 8;
             float m_new = m_run[hh];
 #pragma unroll
-            for (int qq = 0; qq < 4; ++qq) m_new = fmaxf(m_new, part[qq * kTileRows + r]);
+            for (int qq = 0; qq < kParts; ++qq) m_new = fmaxf(m_new, part[qq * kTileRows + r]);
             corr[hh] = m_new == -INFINITY ? 1.f : expf(m_run[hh] - m_new);
             m_run[hh] = m_new;
-        }
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const float p0 = s[j][hh * 2] == -INFINITY ? 0.f : expf(s[j][hh * 2] - m_run[hh]);
-                const float p1 = s[j][hh * 2 + 1] == -INFINITY ? 0.f : expf(s[j][hh * 2 + 1] - m_run[hh]);
-                const __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
-                // the sum runs over the rounded weights, the ones the values are multiplied with
-                sum[hh] += __bfloat162float(pr.x) + __bfloat162float(pr.y);
-                *reinterpret_cast<__nv_bfloat162*>(p_s + (rg * 16 + g + hh * 8) * (kPageTokens + kPad) + quarter * 16 + j * 8 + t * 2) = pr;
-            }
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
+            const float p0 = s[hh * 2] == -INFINITY ? 0.f : expf(s[hh * 2] - m_new);
+            const float p1 = s[hh * 2 + 1] == -INFINITY ? 0.f : expf(s[hh * 2 + 1] - m_new);
+            const __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+            // the sum runs over the rounded weights, the ones the values are multiplied with
+            sum[hh] = __bfloat162float(pr.x) + __bfloat162float(pr.y);
+            *reinterpret_cast<__nv_bfloat162*>(p_s + r * (kPageTokens + kPad) + part_i * 8 + t * 2) = pr;
             sum[hh] += __shfl_xor_sync(0xffffffffu, sum[hh], 1);
             sum[hh] += __shfl_xor_sync(0xffffffffu, sum[hh], 2);
-            if (t == 0) part[4 * kTileRows + quarter * kTileRows + rg * 16 + g + hh * 8] = sum[hh];
+            if (t == 0) part[kParts * kTileRows + part_i * kTileRows + r] = sum[hh];
         }
         __syncthreads();
 #pragma unroll
@@ -308,7 +328,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
             const int r = rg * 16 + g + hh * 8;
             float total = 0.f;
 #pragma unroll
-            for (int qq = 0; qq < 4; ++qq) total += part[4 * kTileRows + qq * kTileRows + r];
+            for (int qq = 0; qq < kParts; ++qq) total += part[kParts * kTileRows + qq * kTileRows + r];
             l_run[hh] = l_run[hh] * corr[hh] + total;
         }
 #pragma unroll
@@ -342,13 +362,12 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
             }
         }
     }
-    cp_async_wait<0>();
     if (n_splits > 1) {
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
             if (pos_r[hh] < 0) continue;
             float* dst = scratch + ((size_t)blockIdx.z * total_rows + (size_t)tok0 * n_heads + r0 + rg * 16 + g + hh * 8) * (rank + 2);
-            if (quarter == 0 && t == 0) { dst[0] = m_run[hh]; dst[1] = l_run[hh]; }
+            if (part_i == 0 && t == 0) { dst[0] = m_run[hh]; dst[1] = l_run[hh]; }
 #pragma unroll
             for (int j = 0; j < NT; ++j)
                 if (j < my_tiles)
@@ -405,9 +424,17 @@ latent_attention_merge_kernel(const float* __restrict__ scratch, bf16* __restric
 
 size_t latent_attention_smem(int D) {
     const size_t ldr = D + kPad;
-    return (kTileRows + 2 * kPageTokens) * ldr * 2 + kTileRows * (kPageTokens + kPad) * 2 + 2 * 4 * kTileRows * 4 + kTileRows * 4;
+    return (kTileRows + 2 * kPageTokens) * ldr * 2 + kTileRows * (kPageTokens + kPad) * 2 + 2 * kParts * kTileRows * 4 + kTileRows * 4 + 16;
 }
 }  // namespace
+
+// 0, or 1 if a block of the attention kernel ever gave up a bounded wait for a staged page
+// (reading it synchronises the device).
+GTG_API int gtg_latent_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_latent_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
 
 // Whether the tensor-core kernel takes rows of D = rank + rot channels with `rank` value channels.
 GTG_API int gtg_latent_attention_supports(int D, int rank) {
@@ -467,9 +494,9 @@ GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo
                             (bf16*)out, ldo, (const bf16*)kc, page_stride, block_table, table_stride, cu_seqlens, slots, \
                             start_pos, n_heads, D, rank, scale, window, n_splits, scratch, total_rows);             \
     } while (0)
-    const int per = ((rank / 8) + 3) / 4;
+    const int per = ((rank / 8) + kParts - 1) / kParts;
     int st = 0;
-    if (per <= 4) GTG_LATENT(4); else if (per <= 8) GTG_LATENT(8); else GTG_LATENT(16);
+    if (per <= 2) GTG_LATENT(2); else if (per <= 4) GTG_LATENT(4); else GTG_LATENT(8);
 #undef GTG_LATENT
     if (st != 0 || n_splits == 1) return st;
     return launch_chained(latent_attention_merge_kernel, dim3(total_rows), dim3(128), 0, stream, (const float*)scratch,

@@ -67,6 +67,7 @@ _SIGNATURES = {
     "gtg_latent_prepare": ("latent", [_I, _P, _I, _P, _I, _P, _P, _F, _P, _L, _P, _I, _P, _P, _P, _P, _I,
                                       _I, _I, _I, _I, _I, _I, _P]),
     "gtg_latent_attention_supports": ("latent", [_I, _I]),
+    "gtg_latent_status": ("latent", []),
     "gtg_latent_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _I, _P]),
     "gtg_latent_attention_splits": ("latent", [_I, _I, _I, _I, _I, _I]),
     "gtg_moe_gather": ("experts", [_P, _I, _P, _I, _P, _I, _I, _P]),
@@ -770,7 +771,7 @@ def bounded_wait_failures() -> int:
     copies (it then returned without a result).  Reading it synchronises."""
     total = 0
     for symbol in ("gtg_gemm_bf16_skinny_status", "gtg_gemm_bf16_tcgen05_status", "gtg_gemm_bf16_swapab_status",
-                   "gtg_attention_tcgen05_status"):
+                   "gtg_attention_tcgen05_status", "gtg_latent_status"):
         if _SIGNATURES[symbol][0] in build._LOADED:        # only libraries that have run can have failed
             total += int(_fn(symbol)())
     return total

@@ -299,6 +299,7 @@ def test_tensor_core_attention_over_latent_rows(heads, row, rank, window):
                 want = (w / w.sum(-1, keepdims=True)) @ r[lo:pos + 1, :rank]
                 assert np.abs(got[at + i] - want).max() <= 2e-2 * max(1.0, np.abs(want).max()), (a, i, np.abs(got[at + i] - want).max())
             at += n
+    assert ops.bounded_wait_failures() == 0                    # no block gave up waiting for a staged page
 
 
 def _latent_mixer(dtype, m, hidden, weights, own_kv=True):
