@@ -204,6 +204,9 @@ class StepContext:
     # set by a block whose norm takes a sublayer's update in float32: a part whose last step
     # leaves float sums may then return them unrounded instead of in the compute dtype
     float_updates: bool = False
+    # with float_updates: a bias (float32 [H]) that the part leaves for the block's norm kernel to add to
+    # the update it returns, instead of adding it itself; the block takes it and sets this None again
+    update_bias: Optional[torch.Tensor] = None
     step: int = 0               # which step of the model this is (counted by the model; for `op_hook`)
     layer: int = -1             # the layer that is running (set by the engine before each block)
     op_hook: Optional[Callable[[int, int, str, torch.Tensor], None]] = None

@@ -17,7 +17,8 @@ stands on a sublayer's output and the sublayers read the hidden state itself
 kind ``rmsnorm`` (the one norm whose fused form with the addition exists).  A
 sublayer's update may be float32 or of the compute dtype; norm and addition are
 float32, and the kernel that adds also leaves the rounded hidden state for the
-next sublayer (`ResidualStream.image`).  Nothing is left pending.  The reference
+next sublayer (`ResidualStream.image`); a part may leave the bias of its last
+projection for that kernel to add (`StepContext.update_bias`).  Nothing is left pending.  The reference
 has no such arrangement.
 
 ``concat_projection``: x <- W [x | kept], a projection of the hidden state side
@@ -105,7 +106,8 @@ class OutputNormBlock(Block):
         image = None
         if ctx.rt.dtype != torch.float32:
             image = ctx.rt.empty(*stream.residual.shape)
-        ops.rmsnorm_add(update, norm.weight, norm.eps, stream.residual, image)
+        bias, ctx.update_bias = ctx.update_bias, None       # a bias the part left for this kernel to add
+        ops.rmsnorm_add(update, norm.weight, norm.eps, stream.residual, image, bias=bias)
         stream.image = image
 
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: CacheHandle) -> None:

@@ -111,6 +111,10 @@ class SwiGLU(FeedForward):
         ctx.trace("gate_act", act)
         sums = rt.empty(n, self.hidden, dtype=torch.float32)
         ops.linear(act, self.w_down, sums)
+        if ctx.float_updates and ctx.op_hook is None:
+            # the block's norm kernel takes float sums and adds the bias itself
+            ctx.update_bias = self.biases[2]
+            return sums
         out = rt.empty(n, self.hidden, dtype=torch.float32 if ctx.float_updates else None)
         ops.add_bias(sums, self.biases[2], out)
         return out

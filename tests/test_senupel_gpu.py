@@ -192,8 +192,9 @@ def test_norm_of_an_update_added_to_the_hidden_state(dtype, float_update):
         residual = t32(res)
         update = t32(upd) if float_update else t32(upd).to(TORCH[dtype])
         image = torch.empty(n, h, dtype=TORCH[dtype], device=DEV)
-        ops.rmsnorm_add(update, t32(w), 1e-3, residual, image)
-        want = res.astype(np.float32) + plain.rms_norm(f64(update), w.astype(np.float32), 1e-3)
+        bias = t32(rng.standard_normal(h)) if float_update else None
+        ops.rmsnorm_add(update, t32(w), 1e-3, residual, image, bias=bias)
+        want = res.astype(np.float32) + plain.rms_norm(f64(update) + (f64(bias) if float_update else 0.0), w.astype(np.float32), 1e-3)
         close(residual, want, "float32", (n, h))                 # norm and sum are float32 in both
         assert torch.equal(image, residual.to(TORCH[dtype]))
 
@@ -433,10 +434,10 @@ def test_gated_feed_forward_with_biases(dtype):
         want = plain.gated_ff(f64(x), w64["gate"], w64["up"], w64["down"], w64["gate.b"], w64["up.b"], w64["down.b"])
         ctx = context(rt, [n], [0], [0])
         close(part.forward(x, ctx), want, dtype, (n, hidden, ff))
-        ctx.float_updates = True
+        ctx.float_updates = True                          # a block whose norm kernel takes float sums and adds the bias
         out = part.forward(x, ctx)
-        assert out.dtype == torch.float32
-        close(out, want, dtype, "float update")
+        assert out.dtype == torch.float32 and ctx.update_bias is not None
+        close(out + ctx.update_bias, want, dtype, "float update, bias left to the norm kernel")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
