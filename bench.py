@@ -477,7 +477,7 @@ def senupel_shape(width, heads, ff, experts, expert_ff, top, window=4096, vocab=
     def mixer(i):
         m = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
              "mask": {"size": window},
-             "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+             "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
         if i % 2:
             m["kv_from"] = i - 1
         return m
