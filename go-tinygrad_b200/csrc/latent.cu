@@ -119,6 +119,7 @@ GTG_API int gtg_latent_prepare(int dtype, const void* q, int ldq, const void* dk
 // 0, or 1 if a block ever gave up waiting for a page it had asked for (it then went on with
 // whatever the buffer held: the result of that launch is not to be used).
 __device__ int g_latent_status = 0;
+static bool g_latent_test_waits = false;       // set by the test hook
 
 namespace {
 constexpr unsigned kPageWaitLimit = 1u << 22;      // polls of a page's barrier before a block gives up
@@ -130,8 +131,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Polls until the phase with `parity` completes or the limit is hit (then the status word is set).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (unsigned i = 0; i < kPageWaitLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned limit) {
+    for (unsigned i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
                      "selp.u32 %0, 1, 0, p;\n}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
@@ -158,7 +159,9 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
                             const bf16* __restrict__ kc, long long page_stride, const int* __restrict__ block_table,
                             int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                             const int* __restrict__ start_pos, int n_heads, int D, int rank, float scale, int window,
-                            int n_splits, float* __restrict__ scratch, int total_rows) {
+                            int n_splits, float* __restrict__ scratch, int total_rows, int test_waits) {
+    // test_waits (the test hook's form of the launch): no page is ever copied and a wait polls a thousand
+    // times, so that every wait runs out, the status word is set and the block still returns
     chain_release();
     chain_wait();
     extern __shared__ __align__(128) unsigned char smem[];
@@ -176,6 +179,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
     float* part = reinterpret_cast<float*>(p_s + kTileRows * (kPageTokens + kPad));   // [2][8][32]: maxima, sums
     int* row_pos = reinterpret_cast<int*>(part + 2 * kParts * kTileRows);                  // [32] position or -1
     const uint32_t bars = smem_u32(row_pos + kTileRows);        // two barriers of 8 bytes: a staged page has arrived
+    volatile int* gave_up = row_pos + kTileRows + 4;            // set by a thread whose wait ran out
     const int start = start_pos[b];
     const int* table = block_table + (size_t)slots[b] * table_stride;
     const int last_row = min(r0 + kTileRows, n_new * n_heads) - 1;
@@ -213,6 +217,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
     // A page is staged by the copy engine, a row a copy (64 copies, two a lane of warp 0), so that no
     // warp that multiplies waits in a queue of copies; the page's barrier counts the bytes.
     if (tid == 0) {
+        *gave_up = 0;
         mbar_init(bars, 1);
         mbar_init(bars + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
@@ -224,6 +229,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
         const uint32_t dst = smem_u32(page_s + (size_t)buf * kPageTokens * ldr);
         if (lane == 0) mbar_expect_tx(bars + 8 * buf, (uint32_t)(kPageTokens * D * 2));
         __syncwarp();
+        if (test_waits) return;
         for (int r = lane; r < kPageTokens; r += 32)
             bulk_row(dst + (uint32_t)(r * ldr * 2), src + (size_t)r * D, (uint32_t)(D * 2), bars + 8 * buf);
     };
@@ -256,8 +262,11 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
         const int p = page_lo + i;
         const int buf = i & 1;
         if (i > 0) __syncthreads();                             // everyone is done with the page before and its weights
+        // A wait ran out: the block stops asking and waiting (a barrier whose phase never completed must
+        // not be armed again) and goes on to its end with what it has; everyone sees the flag alike here.
+        if (*gave_up) break;
         if (i + 1 < n_pages) load_page(buf ^ 1, p + 1);
-        mbar_wait(bars + 8 * buf, ((uint32_t)i >> 1) & 1u);     // page p has arrived
+        if (!mbar_wait(bars + 8 * buf, ((uint32_t)i >> 1) & 1u, test_waits ? 1024u : kPageWaitLimit)) *gave_up = 1;   // else page p has arrived
         if (i == 0) __syncthreads();                            // and everyone's share of the query rows
         const bf16* pg = page_s + (size_t)buf * kPageTokens * ldr;
         // S: rows rg*16.., keys part_i*8.. of the page
@@ -424,7 +433,7 @@ latent_attention_merge_kernel(const float* __restrict__ scratch, bf16* __restric
 
 size_t latent_attention_smem(int D) {
     const size_t ldr = D + kPad;
-    return (kTileRows + 2 * kPageTokens) * ldr * 2 + kTileRows * (kPageTokens + kPad) * 2 + 2 * kParts * kTileRows * 4 + kTileRows * 4 + 16;
+    return (kTileRows + 2 * kPageTokens) * ldr * 2 + kTileRows * (kPageTokens + kPad) * 2 + 2 * kParts * kTileRows * 4 + kTileRows * 4 + 32;
 }
 }  // namespace
 
@@ -434,6 +443,16 @@ GTG_API int gtg_latent_status() {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_latent_status, sizeof(int)) != cudaSuccess) return -1;
     return v;
+}
+
+// For tests of the give-up path only: while set, the attention kernel is launched in its test form
+// (see the kernel).  The call synchronises the device and clears the status word.
+GTG_API int gtg_latent_test_hooks(int test_waits) {
+    const int zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    g_latent_test_waits = test_waits != 0;
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_latent_status, &zero, sizeof(zero));
+    return (int)e;
 }
 
 // Whether the tensor-core kernel takes rows of D = rank + rot channels with `rank` value channels.
@@ -492,7 +511,8 @@ GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo
         }                                                                                                           \
         st = launch_chained(latent_attention_mma_kernel<NT>, grid, dim3(kLatThreads), smem, stream, (const bf16*)q, ldq, \
                             (bf16*)out, ldo, (const bf16*)kc, page_stride, block_table, table_stride, cu_seqlens, slots, \
-                            start_pos, n_heads, D, rank, scale, window, n_splits, scratch, total_rows);             \
+                            start_pos, n_heads, D, rank, scale, window, n_splits, scratch, total_rows,              \
+                            g_latent_test_waits ? 1 : 0);                                                          \
     } while (0)
     const int per = ((rank / 8) + kParts - 1) / kParts;
     int st = 0;

@@ -68,6 +68,7 @@ _SIGNATURES = {
                                       _I, _I, _I, _I, _I, _I, _P]),
     "gtg_latent_attention_supports": ("latent", [_I, _I]),
     "gtg_latent_status": ("latent", []),
+    "gtg_latent_test_hooks": ("latent", [_I]),
     "gtg_latent_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _I, _P]),
     "gtg_latent_attention_splits": ("latent", [_I, _I, _I, _I, _I, _I]),
     "gtg_moe_gather": ("experts", [_P, _I, _P, _I, _P, _I, _I, _P]),
@@ -777,7 +778,7 @@ def bounded_wait_failures() -> int:
     return total
 
 
-WAITING_LIBRARIES = ("gemm_bf16_skinny", "gemm_bf16_tcgen05", "gemm_bf16_swapab", "attention_tcgen05")
+WAITING_LIBRARIES = ("gemm_bf16_skinny", "gemm_bf16_tcgen05", "gemm_bf16_swapab", "attention_tcgen05", "latent")
 
 
 def wait_test_hooks(library: str, test_waits: bool) -> None:

@@ -58,6 +58,35 @@ def prompt_attention():
     return run, want, dict(rtol=2e-2, atol=2e-2)
 
 
+def latent_attention():
+    """Attention over latent rows (one shared head, the values its leading channels): a prompt and a portion."""
+    from go_tinygrad_b200.cache import Cache, KVRequest
+    heads, row, rank, new, starts = 4, 96, 64, [150, 20], [0, 70]
+    cache = Cache([[KVRequest(1, row, None, planes=1)]], [None], max_tokens=64 * 6, max_slots=3, dtype=BF16, device=torch.device(DEV))
+    slots = [cache.open_sequence() for _ in new]
+    cache.reserve_many([(s, a + n) for s, a, n in zip(slots, starts, new)]); cache.flush_tables()
+    kv = cache.handles[0].kv
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    q = rnd(sum(new), heads * row, dtype=BF16, seed=5, scale=0.5)
+    want, at = [], 0
+    for b, (s, a, n) in enumerate(zip(slots, starts, new)):
+        rows = rnd(a + n, row, dtype=BF16, seed=6 + b)
+        for p0 in range(0, a + n, 64):
+            kv.k[int(cache.groups[0].table_host[s][p0 // 64]), 0, : min(64, a + n - p0)] = rows[p0:p0 + 64]
+        for i in range(n):
+            sc = q[at + i].double().view(heads, row) @ rows[: a + i + 1].double().T * 0.1
+            want.append((torch.softmax(sc, dim=-1) @ rows[: a + i + 1, :rank].double()).reshape(-1))
+        at += n
+    want = torch.stack(want).float()
+
+    def run():
+        out = torch.full((sum(new), heads * rank), 7.0, dtype=BF16, device=DEV)
+        ops.latent_attention_bf16(q, out, kv, i32([0, new[0], sum(new)]), i32(slots), i32(starts), 2, max(new), heads, rank, 0.1, 0)
+        return out.float()
+    run.keep = cache
+    return run, want, dict(rtol=2e-2, atol=2e-2)
+
+
 CASES = {
     # library -> what runs its kernels: (how to build the case)
     "gemm_bf16_tcgen05": [lambda: product("tcgen05", 300, 520, 1024), residual_product],
@@ -68,6 +97,7 @@ CASES = {
                          lambda: product("skinny", 3, 50, 8200),         # an inner size that takes the row-copy kernel,
                          lambda: product("skinny", 5, 96, 264)],         # ... with a cluster of ranks and with one
     "attention_tcgen05": [prompt_attention],
+    "latent": [latent_attention],
 }
 
 
