@@ -15,7 +15,9 @@
 //   * with a down projection: the norm of the latent, the rotation of the shared
 //     key part, and the store of both into the token's cache row;
 //   * the rotation of every head's b_h into the tail of the head's query row
-//     (the head of the row is written by the product with U_h^T).
+//     (the head of the row is written by the product with U_h^T), or, without
+//     such rows (q_full null), in place.
+// rows_out, if given, receives the token's cache row once more, token by token.
 // Rotation: of the part's first `rdims` channels, (2i, 2i+1) turn by the angle of pair i, whose cosine and
 // sine (amplitude included) come from the step's table [token, rot/2].
 #include "mma_helpers.cuh"
@@ -24,12 +26,12 @@
 namespace {
 template <typename T>
 __global__ void __launch_bounds__(128)
-latent_prepare_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ dkv, int ldd,
+latent_prepare_kernel(T* __restrict__ q, int ldq, const T* __restrict__ dkv, int ldd,
                       const float2* __restrict__ cos_sin, const float* __restrict__ norm_w, float eps,
                       T* __restrict__ kc, long long page_stride, const int* __restrict__ block_table,
                       int table_stride, const int* __restrict__ token_seq, const int* __restrict__ slots,
                       const int* __restrict__ positions, T* __restrict__ q_full, int ldf,
-                      int n_heads, int dim, int rot, int rdims, int rank) {
+                      int n_heads, int dim, int rot, int rdims, int rank, T* __restrict__ rows_out, int ldo) {
     chain_release();
     chain_wait();
     __shared__ float scratch[33];
@@ -49,15 +51,34 @@ latent_prepare_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ dk
         const int slot = slots[token_seq[n]];
         const int page = block_table[(size_t)slot * table_stride + pos / kPageTokens];
         T* row = kc + (size_t)page * page_stride + (size_t)(pos % kPageTokens) * (rank + rot);
-        for (int i = threadIdx.x; i < rank; i += blockDim.x)
+        T* copy = rows_out ? rows_out + (size_t)n * ldo : nullptr;      // the same row, token by token, for the step's own use
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) {
             row[i] = from_f32<T>((norm_w[i] * to_f32<T>(d[i])) * s);
+            if (copy) copy[i] = row[i];
+        }
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             const float u = to_f32<T>(d[rank + 2 * i]), v = to_f32<T>(d[rank + 2 * i + 1]);
             const float2 a = cs[i];
             row[rank + 2 * i] = from_f32<T>(u * a.x - v * a.y);
             row[rank + 2 * i + 1] = from_f32<T>(v * a.x + u * a.y);
+            if (copy) { copy[rank + 2 * i] = row[rank + 2 * i]; copy[rank + 2 * i + 1] = row[rank + 2 * i + 1]; }
         }
-        for (int i = rdims + threadIdx.x; i < rot; i += blockDim.x) row[rank + i] = d[rank + i];
+        for (int i = rdims + threadIdx.x; i < rot; i += blockDim.x) {
+            row[rank + i] = d[rank + i];
+            if (copy) copy[rank + i] = d[rank + i];
+        }
+    }
+    if (!q_full) {
+        // the rotated parts go back where they came from: the query rows stay [a_h | b_h'] per head
+        for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+            const int h = idx / half, i = idx % half;
+            T* p = q + (size_t)n * ldq + (size_t)h * (dim + rot) + dim;
+            const float u = to_f32<T>(p[2 * i]), v = to_f32<T>(p[2 * i + 1]);
+            const float2 a = cs[i];
+            p[2 * i] = from_f32<T>(u * a.x - v * a.y);
+            p[2 * i + 1] = from_f32<T>(v * a.x + u * a.y);
+        }
+        return;
     }
     const int D = rank + rot;
     for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
@@ -76,24 +97,24 @@ latent_prepare_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ dk
 }
 }  // namespace
 
-GTG_API int gtg_latent_prepare(int dtype, const void* q, int ldq, const void* dkv, int ldd, const float* cos_sin,
+GTG_API int gtg_latent_prepare(int dtype, void* q, int ldq, const void* dkv, int ldd, const float* cos_sin,
                                const float* norm_w, float eps, void* kc, long long page_stride,
                                const int* block_table, int table_stride, const int* token_seq, const int* slots,
                                const int* positions, void* q_full, int ldf, int N, int n_heads, int dim, int rot,
-                               int rdims, int rank, cudaStream_t stream) {
+                               int rdims, int rank, void* rows_out, int ldo, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (n_heads <= 0 || dim <= 0 || rot <= 0 || rdims < 0 || rdims > rot || rdims % 2 || rank <= 0) return kErrBadArgument;
     if (dkv && (!kc || !norm_w || !block_table)) return kErrBadArgument;
     if (dtype == 0)
-        return launch_chained(latent_prepare_kernel<float>, dim3(N), dim3(128), 0, stream, (const float*)q, ldq,
+        return launch_chained(latent_prepare_kernel<float>, dim3(N), dim3(128), 0, stream, (float*)q, ldq,
                               (const float*)dkv, ldd, (const float2*)cos_sin, norm_w, eps, (float*)kc, page_stride,
                               block_table, table_stride, token_seq, slots, positions, (float*)q_full, ldf, n_heads,
-                              dim, rot, rdims, rank);
+                              dim, rot, rdims, rank, (float*)rows_out, ldo);
     if (dtype == 1)
-        return launch_chained(latent_prepare_kernel<bf16>, dim3(N), dim3(128), 0, stream, (const bf16*)q, ldq,
+        return launch_chained(latent_prepare_kernel<bf16>, dim3(N), dim3(128), 0, stream, (bf16*)q, ldq,
                               (const bf16*)dkv, ldd, (const float2*)cos_sin, norm_w, eps, (bf16*)kc, page_stride,
                               block_table, table_stride, token_seq, slots, positions, (bf16*)q_full, ldf, n_heads,
-                              dim, rot, rdims, rank);
+                              dim, rot, rdims, rank, (bf16*)rows_out, ldo);
     return kErrBadArgument;
 }
 
@@ -521,4 +542,247 @@ GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo
     if (st != 0 || n_splits == 1) return st;
     return launch_chained(latent_attention_merge_kernel, dim3(total_rows), dim3(128), 0, stream, (const float*)scratch,
                           (bf16*)out, ldo, n_heads, rank, n_splits, total_rows);
+}
+
+// ---- prompts that start their sequences: keys and values expanded per head ---------------
+// When every sequence of a step starts at its first token, the step's own rows are all the keys
+// there are, and expanding them per head (K_h = U_h c, V_h = V_h c: two products over the step's
+// latents) costs less than attending in the folded form: dim + rot channels per score and vdim
+// per value instead of rank + rot and rank.  This kernel is the attention over those expanded
+// rows: q [N, heads, dim + rot] (rotated part last, already rotated), kn [N, heads, dim], the
+// shared rotated key part kr [N, rot] (row stride ldr), v [N, heads, vdim] -> out [N, heads,
+// vdim].  One block of four warps per (64 queries, head, sequence); a warp owns 16 query rows
+// with their fragments in registers, walks tiles of 64 keys staged by cp.async (two in flight),
+// S and the streaming softmax (float, expf) stay in its registers, the weights become the
+// left operand of the value product without leaving them, O stays in registers.  Causal, window
+// as everywhere.  KS = (dim + rot) / 16 and NV = vdim / 8 at most (template), dim and rot
+// multiples of 16, vdim of 8.
+namespace {
+constexpr int kQTile = 64, kKTile = 64, kExpThreads = 128;
+
+template <int KS, int NV>
+__global__ void __launch_bounds__(kExpThreads)
+expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kn, int ldk,
+                          const bf16* __restrict__ kr, int ldr, const bf16* __restrict__ v, int ldv,
+                          bf16* __restrict__ out, int ldo, const int* __restrict__ cu_seqlens,
+                          int dim, int rot, int vdim, float scale, int window) {
+    chain_release();
+    chain_wait();
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int tok0 = cu_seqlens[b], len = cu_seqlens[b + 1] - tok0;
+    const int q0 = blockIdx.x * kQTile;
+    if (q0 >= len) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int dk = dim + rot;
+    const int ldks = dk + kPad, ldvs = vdim + kPad;             // staged rows, in elements
+    bf16* k_s = reinterpret_cast<bf16*>(smem);                  // [2][64][ldks]; the first buffer holds the queries at the start
+    bf16* v_s = k_s + 2 * kKTile * ldks;                        // [2][64][ldvs]
+    const int n_ks = dk / 16, n_nv = vdim / 8;
+    const int kc_n = dim / 8, kc_r = rot / 8, vc = vdim / 8;    // 16-byte chunks per row
+
+    // the queries: staged, then each warp's 16 rows into registers
+    for (int r = warp; r < kQTile; r += kExpThreads / 32) {
+        const bool ok = q0 + r < len;
+        const bf16* src = q + (size_t)(tok0 + (ok ? q0 + r : 0)) * ldq + (size_t)h * dk;
+        for (int c = lane; c < dk / 8; c += 32) cp_async16(smem_u32(k_s + r * ldks + c * 8), src + c * 8, ok ? 16 : 0);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    uint32_t qf[KS][4];
+    {
+        const uint32_t a_addr = smem_u32(k_s + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldks + (lane >> 4) * 8);
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+            if (ks < n_ks) ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], a_addr + ks * 32);
+    }
+    __syncthreads();                                            // the queries' place is free for keys
+
+    const int q_hi = min(q0 + kQTile, len) - 1;
+    const int lo_min = (window > 0 && q0 - window + 1 > 0) ? q0 - window + 1 : 0;
+    const int t_lo = lo_min / kKTile, t_hi = q_hi / kKTile;
+    auto load_tile = [&](int buf, int kt) {
+        bf16* kd = k_s + (size_t)buf * kKTile * ldks;
+        bf16* vd = v_s + (size_t)buf * kKTile * ldvs;
+        for (int r = warp; r < kKTile; r += kExpThreads / 32) {
+            const int key = kt * kKTile + r;
+            const bool ok = key < len;
+            const size_t row = (size_t)(tok0 + (ok ? key : 0));
+            const bf16* sn = kn + row * ldk + (size_t)h * dim;
+            const bf16* sr = kr + row * ldr;
+            const bf16* sv = v + row * ldv + (size_t)h * vdim;
+            for (int c = lane; c < kc_n; c += 32) cp_async16(smem_u32(kd + r * ldks + c * 8), sn + c * 8, ok ? 16 : 0);
+            for (int c = lane; c < kc_r; c += 32) cp_async16(smem_u32(kd + r * ldks + dim + c * 8), sr + c * 8, ok ? 16 : 0);
+            for (int c = lane; c < vc; c += 32) cp_async16(smem_u32(vd + r * ldvs + c * 8), sv + c * 8, ok ? 16 : 0);
+        }
+    };
+    load_tile(0, t_lo);
+    cp_async_commit();
+
+    float o[NV][4];
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    int pos_r[2], lo_r[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int r = q0 + warp * 16 + g + hh * 8;
+        pos_r[hh] = r < len ? r : -1;
+        lo_r[hh] = (window > 0 && r - window + 1 > 0) ? r - window + 1 : 0;
+    }
+
+    for (int kt = t_lo; kt <= t_hi; ++kt) {
+        const int buf = (kt - t_lo) & 1;
+        if (kt > t_lo) __syncthreads();                         // everyone is done with the tile before
+        if (kt + 1 <= t_hi) load_tile(buf ^ 1, kt + 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();                                        // tile kt staged
+        const bf16* kd = k_s + (size_t)buf * kKTile * ldks;
+        const bf16* vd = v_s + (size_t)buf * kKTile * ldvs;
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+        {
+            const uint32_t b_addr = smem_u32(kd + ((lane & 7) + (lane >> 4) * 8) * ldks + ((lane >> 3) & 1) * 8);
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                if (ks < n_ks) {
+                    uint32_t bfr[4][4];
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj)
+                        ldmatrix_x4(bfr[jj][0], bfr[jj][1], bfr[jj][2], bfr[jj][3], b_addr + (jj * 16 * ldks + ks * 16) * 2);
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        mma_bf16_16816(s[2 * jj], qf[ks], bfr[jj][0], bfr[jj][1]);
+                        mma_bf16_16816(s[2 * jj + 1], qf[ks], bfr[jj][2], bfr[jj][3]);
+                    }
+                }
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int hh = e >> 1;
+                const int key = kt * kKTile + j * 8 + t * 2 + (e & 1);
+                const bool seen = pos_r[hh] >= 0 && key <= pos_r[hh] && key >= lo_r[hh];
+                s[j][e] = seen ? s[j][e] * scale : -INFINITY;
+                mx[hh] = fmaxf(mx[hh], s[j][e]);
+            }
+        float corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
+            const float m_new = fmaxf(m_run[hh], mx[hh]);
+            corr[hh] = m_new == -INFINITY ? 1.f : expf(m_run[hh] - m_new);
+            m_run[hh] = m_new;
+        }
+        uint32_t pf[4][4];                                      // the weights as left operand: 4 steps of 16 keys
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) p[e] = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - m_run[e >> 1]);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(p[0], p[1]), hi = __floats2bfloat162_rn(p[2], p[3]);
+            // the sums run over the rounded weights, the ones the values are multiplied with
+            sum[0] += __bfloat162float(lo.x) + __bfloat162float(lo.y);
+            sum[1] += __bfloat162float(hi.x) + __bfloat162float(hi.y);
+            pf[j >> 1][(j & 1) * 2] = *reinterpret_cast<const uint32_t*>(&lo);
+            pf[j >> 1][(j & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            sum[hh] += __shfl_xor_sync(0xffffffffu, sum[hh], 1);
+            sum[hh] += __shfl_xor_sync(0xffffffffu, sum[hh], 2);
+            l_run[hh] = l_run[hh] * corr[hh] + sum[hh];
+        }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
+        }
+        {
+            const uint32_t v_addr = smem_u32(vd + ((lane & 7) + ((lane >> 3) & 1) * 8) * ldvs + (lane >> 4) * 8);
+#pragma unroll
+            for (int ks = 0; ks < kKTile / 16; ++ks) {
+#pragma unroll
+                for (int c = 0; c < NV; c += 8) {
+                    uint32_t vf[4][4];
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2)
+                        if (c + j < n_nv)
+                            ldmatrix_x4_trans(vf[j / 2][0], vf[j / 2][1], vf[j / 2][2], vf[j / 2][3], v_addr + (ks * 16 * ldvs + (c + j) * 8) * 2);
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2)
+                        if (c + j < n_nv) {
+                            mma_bf16_16816(o[c + j], pf[ks], vf[j / 2][0], vf[j / 2][1]);
+                            if (c + j + 1 < NV) mma_bf16_16816(o[c + j + 1], pf[ks], vf[j / 2][2], vf[j / 2][3]);
+                        }
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        if (pos_r[hh] < 0 || l_run[hh] <= 0.f) continue;
+        const float inv = 1.0f / l_run[hh];
+        bf16* dst = out + (size_t)(tok0 + pos_r[hh]) * ldo + (size_t)h * vdim + t * 2;
+#pragma unroll
+        for (int j = 0; j < NV; ++j)
+            if (j < n_nv)
+                *reinterpret_cast<__nv_bfloat162*>(dst + j * 8) = __floats2bfloat162_rn(o[j][hh * 2] * inv, o[j][hh * 2 + 1] * inv);
+    }
+}
+
+size_t expanded_attention_smem(int dk, int vdim) {
+    return (size_t)2 * kKTile * ((dk + kPad) + (vdim + kPad)) * 2;
+}
+}  // namespace
+
+GTG_API int gtg_expanded_attention_supports(int dim, int rot, int vdim) {
+    return dim > 0 && rot > 0 && vdim > 0 && dim % 16 == 0 && rot % 16 == 0 && vdim % 8 == 0 && dim + rot <= 256 && vdim <= 128;
+}
+
+// Attention of a step whose sequences all start at their first token, over the step's own rows expanded per head.
+GTG_API int gtg_expanded_attention_bf16(const void* q, int ldq, const void* kn, int ldk, const void* kr, int ldr,
+                                        const void* v, int ldv, void* out, int ldo, const int* cu_seqlens, int n_seqs,
+                                        int max_q_len, int n_heads, int dim, int rot, int vdim, float scale, int window,
+                                        cudaStream_t stream) {
+    if (n_seqs <= 0 || max_q_len <= 0) return 0;
+    if (n_heads <= 0) return kErrBadArgument;
+    if (!gtg_expanded_attention_supports(dim, rot, vdim)) return kErrUnsupported;
+    if (ldq % 8 || ldk % 8 || ldr % 8 || ldv % 8 || ldo % 2 || ((uintptr_t)q % 16) || ((uintptr_t)kn % 16) || ((uintptr_t)kr % 16) ||
+        ((uintptr_t)v % 16) || ((uintptr_t)out % 4))
+        return kErrUnsupported;
+    if (n_heads > 65535 || n_seqs > 65535) return kErrUnsupported;
+    const size_t smem = expanded_attention_smem(dim + rot, vdim);
+    const dim3 grid((max_q_len + kQTile - 1) / kQTile, n_heads, n_seqs);
+#define GTG_EXPANDED(KS, NV)                                                                                        \
+    do {                                                                                                            \
+        static bool configured = false;                                                                             \
+        if (!configured) {                                                                                          \
+            const cudaError_t e = cudaFuncSetAttribute(expanded_attention_kernel<KS, NV>,                           \
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);    \
+            if (e != cudaSuccess) return (int)e;                                                                    \
+            configured = true;                                                                                      \
+        }                                                                                                           \
+        return launch_chained(expanded_attention_kernel<KS, NV>, grid, dim3(kExpThreads), smem, stream, (const bf16*)q, ldq, \
+                              (const bf16*)kn, ldk, (const bf16*)kr, ldr, (const bf16*)v, ldv, (bf16*)out, ldo, cu_seqlens, \
+                              dim, rot, vdim, scale, window);                                                       \
+    } while (0)
+    const int ks = (dim + rot) / 16;
+    if (vdim <= 64) {
+        if (ks <= 4) GTG_EXPANDED(4, 8); else if (ks <= 8) GTG_EXPANDED(8, 8); else if (ks <= 12) GTG_EXPANDED(12, 8); else GTG_EXPANDED(16, 8);
+    }
+    if (ks <= 4) GTG_EXPANDED(4, 16); else if (ks <= 8) GTG_EXPANDED(8, 16); else if (ks <= 12) GTG_EXPANDED(12, 16); else GTG_EXPANDED(16, 16);
+#undef GTG_EXPANDED
 }

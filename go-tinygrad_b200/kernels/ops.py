@@ -65,7 +65,9 @@ _SIGNATURES = {
     "gtg_gemm_bf16_grouped": ("gemm_bf16_grouped", [_P, _I, _L, _P, _I, _P, _I, _L, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I,
                                                     _I, _P, _I, _L, _P]),
     "gtg_latent_prepare": ("latent", [_I, _P, _I, _P, _I, _P, _P, _F, _P, _L, _P, _I, _P, _P, _P, _P, _I,
-                                      _I, _I, _I, _I, _I, _I, _P]),
+                                      _I, _I, _I, _I, _I, _I, _P, _I, _P]),
+    "gtg_expanded_attention_supports": ("latent", [_I, _I, _I]),
+    "gtg_expanded_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]),
     "gtg_latent_attention_supports": ("latent", [_I, _I]),
     "gtg_latent_status": ("latent", []),
     "gtg_latent_test_hooks": ("latent", [_I]),
@@ -944,19 +946,28 @@ def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: flo
 
 # ---------------------------------------------------------- attention through a latent
 def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], cos_sin: torch.Tensor, norm_weight: Optional[torch.Tensor],
-                   eps: float, kv, token_seq, slots, positions, q_full: torch.Tensor, n_heads: int, dim: int,
-                   rot: int, rank: int) -> None:
+                   eps: float, kv, token_seq, slots, positions, q_full: Optional[torch.Tensor], n_heads: int, dim: int,
+                   rot: int, rank: int, rows_out: Optional[torch.Tensor] = None) -> None:
     """Per token: with a down projection `dkv` [N, rank + rot], the latent
     rmsnorm(dkv[:, :rank]) * norm_weight and the rotated dkv[:, rank:] go into the
     token's cache row [rank + rot] of `kv`; and every head's rotated query part
     q[:, h, dim:] goes to q_full[:, h, rank:] (q [N, heads * (dim + rot)], q_full
     [N, heads * (rank + rot)]).  Of a rotated part's channels the first 2 P turn,
-    pairs (2i, 2i+1) by cos_sin [N, P, 2]; the rest pass unchanged."""
-    _rows2d(q, "latent_prepare: q"); _rows2d(q_full, "latent_prepare: q_full")
+    pairs (2i, 2i+1) by cos_sin [N, P, 2]; the rest pass unchanged.  Without q_full the
+    rotated query parts are written back into q.  `rows_out` [N, rank + rot], with a down
+    projection, receives every token's cache row once more, token by token."""
+    _rows2d(q, "latent_prepare: q")
     N = q.shape[0]
     _need(rot % 2 == 0 and rot > 0, "latent_prepare: an even number of rotated channels is needed")
-    _need(q.shape[1] == n_heads * (dim + rot) and tuple(q_full.shape) == (N, n_heads * (rank + rot)) and q.dtype == q_full.dtype,
-          "latent_prepare: q must be [N, heads*(dim+rot)] and q_full [N, heads*(rank+rot)] of one dtype")
+    _need(q.shape[1] == n_heads * (dim + rot), "latent_prepare: q must be [N, heads*(dim+rot)]")
+    if q_full is not None:
+        _rows2d(q_full, "latent_prepare: q_full")
+        _need(tuple(q_full.shape) == (N, n_heads * (rank + rot)) and q.dtype == q_full.dtype,
+              "latent_prepare: q_full must be [N, heads*(rank+rot)] of q's dtype")
+    if rows_out is not None:
+        _rows2d(rows_out, "latent_prepare: rows_out")
+        _need(dkv is not None and tuple(rows_out.shape) == (N, rank + rot) and rows_out.dtype == q.dtype,
+              "latent_prepare: rows_out needs a down projection and must be [N, rank+rot] of q's dtype")
     _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.dim() == 3 and cos_sin.shape[0] == N
           and cos_sin.shape[2] == 2 and 2 * cos_sin.shape[1] <= rot, "latent_prepare: cos_sin must be float32 [N, pairs <= rot/2, 2]")
     rdims = 2 * cos_sin.shape[1]
@@ -974,7 +985,8 @@ def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], cos_sin: torch.
         args = (None, 0, None, 0)
     _check(_fn("gtg_latent_prepare")(_dt(q), _ptr(q), q.stride(0), _ptr(dkv), dkv.stride(0) if dkv is not None else 0,
                                      _ptr(cos_sin), _ptr(norm_weight), float(eps), *args, _ptr(token_seq), _ptr(slots),
-                                     _ptr(positions), _ptr(q_full), q_full.stride(0), N, n_heads, dim, rot, rdims, rank, _stream()),
+                                     _ptr(positions), _ptr(q_full), q_full.stride(0) if q_full is not None else 0, N, n_heads, dim,
+                                     rot, rdims, rank, _ptr(rows_out), rows_out.stride(0) if rows_out is not None else 0, _stream()),
            "latent_prepare")
 
 
@@ -1023,6 +1035,34 @@ def latent_attention_bf16(q: torch.Tensor, out: torch.Tensor, kv, cu_seqlens, sl
                                             int(n_seqs), int(max_q_len), n_heads, kv.head_dim, int(rank), float(scale), int(window),
                                             int(n_splits), _ptr(scratch) if n_splits > 1 else None, q.shape[0], _stream()),
            "latent_attention_bf16")
+
+
+def expanded_attention_supports(dim: int, rot: int, v_dim: int) -> bool:
+    """Whether `expanded_attention_bf16` takes heads of dim + rot key channels and v_dim value channels."""
+    return bool(_fn("gtg_expanded_attention_supports")(int(dim), int(rot), int(v_dim)))
+
+
+def expanded_attention_bf16(q: torch.Tensor, k_plain: torch.Tensor, k_rot: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                            cu_seqlens, n_seqs: int, max_q_len: int, n_heads: int, dim: int, rot: int, v_dim: int,
+                            scale: float, window: int = 0) -> None:
+    """Attention of a step whose sequences all start at their first token, over the
+    step's own rows with keys and values per head: q [N, heads * (dim + rot)] (a
+    head's rotated part last, rotated), k_plain [N, heads * dim], k_rot [N, rot]
+    (one rotated key part for all heads), v [N, heads * v_dim] -> out [N, heads *
+    v_dim].  Causal within each sequence, over the last `window` keys (0: all)."""
+    for name, t in (("q", q), ("k_plain", k_plain), ("k_rot", k_rot), ("v", v), ("out", out)):
+        _rows2d(t, f"expanded_attention: {name}")
+        _need(t.dtype == torch.bfloat16, "expanded_attention_bf16: bfloat16 only")
+    N = q.shape[0]
+    _need(q.shape[1] == n_heads * (dim + rot) and tuple(k_plain.shape) == (N, n_heads * dim) and tuple(k_rot.shape) == (N, rot)
+          and tuple(v.shape) == (N, n_heads * v_dim) and tuple(out.shape) == (N, n_heads * v_dim),
+          "expanded_attention_bf16: shapes do not agree")
+    _need(expanded_attention_supports(dim, rot, v_dim), "expanded_attention_bf16: head sizes not supported")
+    _int32("expanded_attention_bf16", cu_seqlens)
+    _check(_fn("gtg_expanded_attention_bf16")(_ptr(q), q.stride(0), _ptr(k_plain), k_plain.stride(0), _ptr(k_rot), k_rot.stride(0),
+                                              _ptr(v), v.stride(0), _ptr(out), out.stride(0), _ptr(cu_seqlens), int(n_seqs),
+                                              int(max_q_len), n_heads, dim, rot, v_dim, float(scale), int(window), _stream()),
+           "expanded_attention_bf16")
 
 
 # ------------------------------------------------------------------ routed experts

@@ -19,6 +19,14 @@ head of kv_rank + rot_dim channels whose values are its first kv_rank channels;
 a product per head applies V_h to the attended latents.  The cache holds
 kv_rank + rot_dim numbers a token and one plane, whatever the head count.
 
+A step whose sequences all start at their first token (whole prompts, in
+bfloat16) takes another road after the per-token kernel: its own rows are all
+the keys there are, so one product expands them per head (U_h c and V_h c for
+all heads) and attention runs over those, dim + rot channels a score and v_dim a
+value instead of kv_rank + rot_dim and kv_rank.  The layer with the down
+projection leaves the step's rows in the step's shared values for the layers
+that read its cache.
+
 Parameters: ``hidden_size``, ``n_heads``, ``head_dim``, ``rot_dim``, ``v_dim``,
 ``kv_rank``, ``window`` (None: all keys), ``scale`` (None: (head_dim +
 rot_dim)^-1/2), ``eps`` (of the latent's norm), ``position`` (a rotary
@@ -69,7 +77,7 @@ class LatentAttention(Mixer):
         self.row = self.rank + self.rot                     # a cache row, and a folded query row of a head
         self.q_dim = self.n_heads * (self.dim + self.rot)
         self.g_dim = self.n_heads * self.v_dim if gate else 0
-        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.norm_w = None
+        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.norm_w = self.w_expand = None
 
     def weight_specs(self) -> List[WeightSpec]:
         H = self.n_heads
@@ -102,6 +110,10 @@ class LatentAttention(Mixer):
         # U_h^T per head, [H, rank, dim]: the product that folds U_h into the query reads it as its weight
         self.w_uk_t = rt.matrix(tensors[self.names["uk"]].to(rt.dtype).reshape(H, self.dim, self.rank).transpose(1, 2))
         self.w_uv = rt.matrix(tensors[self.names["uv"]]).view(H, self.v_dim, self.rank)
+        # [U; V] for all heads, [H * (dim + v_dim), rank]: the product that expands a prompt's rows per head
+        self.w_expand = None
+        if rt.dtype == torch.bfloat16:
+            self.w_expand = rt.matrix(torch.cat([tensors[self.names["uk"]].to(rt.dtype), tensors[self.names["uv"]].to(rt.dtype)], dim=0))
         self.w_o = rt.matrix(tensors[self.names["o"]])
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheHandle) -> torch.Tensor:
@@ -117,6 +129,8 @@ class LatentAttention(Mixer):
         gate = proj[:, self.q_dim: self.q_dim + self.g_dim] if self.g_dim else None
         dkv = proj[:, self.q_dim + self.g_dim:] if (self.own_kv and cache.writes) else None
         rotation = self.position.rotation(ctx)
+        if self._expands(ctx, cache):
+            return self._forward_expanded(x, ctx, cache, q, gate, dkv, rotation)
         folded = rt.empty(n, H * self.row)
         ops.latent_prepare(q, dkv, rotation, self.norm_w, self.eps, kv, ctx.token_seq, ctx.slots, ctx.positions,
                            folded, H, self.dim, self.rot, self.rank)
@@ -138,4 +152,40 @@ class LatentAttention(Mixer):
         ops.linear_heads(attended.view(n, H, self.rank), self.w_uv, heads.view(n, H, self.v_dim),
                          gate.view(n, H, self.v_dim) if gate is not None else None)
         ctx.trace("attn", heads)
+        return emit_update(heads, self.w_o, ctx)
+
+    # ------------------------------------------------- whole prompts: keys and values per head
+    def _rows_key(self, cache: CacheHandle):
+        return ("latent_rows", cache.kv.k.data_ptr())
+
+    def _expands(self, ctx: StepContext, cache: CacheHandle) -> bool:
+        """Whether this step takes the expanded road: bfloat16, not a decode step, every sequence at its
+        first token (the step's tokens are all the keys), sizes the kernel and the products take, and,
+        for a layer without a down projection, the rows the owning layer left in this step."""
+        return (ctx.rt.dtype == torch.bfloat16 and not ctx.is_decode
+                and ctx.total_kv_len == ctx.n_tokens and self.rank % 8 == 0 and self.row % 8 == 0
+                and (self.n_heads * self.dim) % 8 == 0 and (self.n_heads * self.v_dim) % 8 == 0
+                and ops.expanded_attention_supports(self.dim, self.rot, self.v_dim)
+                and ((self.own_kv and cache.writes) or self._rows_key(cache) in ctx.shared))
+
+    def _forward_expanded(self, x, ctx: StepContext, cache: CacheHandle, q, gate, dkv, rotation):
+        rt = ctx.rt
+        n, H = x.shape[0], self.n_heads
+        if dkv is not None:
+            rows = rt.empty(n, self.row, lifetime="step")
+            ops.latent_prepare(q, dkv, rotation, self.norm_w, self.eps, cache.kv, ctx.token_seq, ctx.slots, ctx.positions,
+                               None, H, self.dim, self.rot, self.rank, rows_out=rows)
+            ctx.shared[self._rows_key(cache)] = rows
+        else:
+            rows = ctx.shared[self._rows_key(cache)]
+            ops.latent_prepare(q, None, rotation, None, self.eps, None, ctx.token_seq, ctx.slots, ctx.positions,
+                               None, H, self.dim, self.rot, self.rank)
+        expanded = rt.empty(n, H * (self.dim + self.v_dim))
+        ops.linear(rows[:, : self.rank], self.w_expand, expanded)
+        heads = rt.empty(n, H * self.v_dim)
+        ops.expanded_attention_bf16(q, expanded[:, : H * self.dim], rows[:, self.rank:], expanded[:, H * self.dim:], heads,
+                                    ctx.cu_seqlens, ctx.n_seqs, ctx.max_q_len, H, self.dim, self.rot, self.v_dim,
+                                    self.scale, self.window or 0)
+        if gate is not None:
+            ops.sigmoid_gate(heads, gate)
         return emit_update(heads, self.w_o, ctx)

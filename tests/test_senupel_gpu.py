@@ -303,6 +303,37 @@ def test_tensor_core_attention_over_latent_rows(heads, row, rank, window):
     assert ops.bounded_wait_failures() == 0                    # no block gave up waiting for a staged page
 
 
+@pytest.mark.parametrize("heads,dim,rot,vdim", [(16, 128, 64, 128), (3, 16, 16, 8), (5, 32, 16, 40), (2, 192, 64, 64), (1, 64, 32, 24)])
+@pytest.mark.parametrize("window", [0, 1, 70, 64])
+def test_attention_over_a_prompt_expanded_per_head(heads, dim, rot, vdim, window):
+    """The bfloat16 kernel for steps whose sequences all start at their first token: keys
+    and values per head, one rotated key part for all heads; sequences of 150, 37, 2, 1
+    and 65 tokens in one batch; against softmax in float64."""
+    rng = np.random.default_rng(heads + dim)
+    lens = [150, 37, 2, 1, 65]
+    n, dk = sum(lens), dim + rot
+    rt = Runtime(DEV, torch.bfloat16)
+    ctx = context(rt, lens, [0] * len(lens), list(range(len(lens))))
+    q = t32(rng.standard_normal((n, heads * dk)) * 0.5).to(torch.bfloat16)
+    wide = t32(rng.standard_normal((n, heads * (dim + vdim)))).to(torch.bfloat16)     # keys and values side by side, as the mixer has them
+    rows = t32(rng.standard_normal((n, 24 + rot))).to(torch.bfloat16)                  # the rotated key part behind 24 other channels
+    kn, v, kr = wide[:, : heads * dim], wide[:, heads * dim:], rows[:, 24:]
+    out = torch.zeros(n, heads * vdim, dtype=torch.bfloat16, device=DEV)
+    scale = 1.3 / np.sqrt(dk)
+    ops.expanded_attention_bf16(q, kn, kr, v, out, ctx.cu_seqlens, len(lens), max(lens), heads, dim, rot, vdim, scale, window)
+    got, at = f64(out).reshape(n, heads, vdim), 0
+    q64, kn64, v64, kr64 = f64(q).reshape(n, heads, dk), f64(kn).reshape(n, heads, dim), f64(v).reshape(n, heads, vdim), f64(kr)
+    for L in lens:
+        for i in range(L):
+            lo = max(0, i - window + 1) if window else 0
+            keys = slice(at + lo, at + i + 1)
+            sc = (np.einsum("hd,khd->hk", q64[at + i, :, :dim], kn64[keys]) + q64[at + i, :, dim:] @ kr64[keys].T) * scale
+            w = np.exp(sc - sc.max(-1, keepdims=True))
+            want = np.einsum("hk,khd->hd", w / w.sum(-1, keepdims=True), v64[keys])
+            assert np.abs(got[at + i] - want).max() <= 2e-2 * max(1.0, np.abs(want).max()), (L, i, np.abs(got[at + i] - want).max())
+        at += L
+
+
 def _latent_mixer(dtype, m, hidden, weights, own_kv=True):
     scaling = m["rot"].get("scaling")
     position = PartSpec("rotary", {"head_dim": m["rot_dim"], "rotary_dim": m["rot"]["dims"], "theta": m["rot"]["base"],
