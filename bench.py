@@ -651,9 +651,19 @@ def run_design(args):
             keys = (ctx_len + per) * n_seqs if per == 1 else sum(min(i + 1, window) for i in range(per))
             splits, floats = ops.latent_attention_plan(n_seqs, per, heads, row, rank, ctx_len + per, window)
             runs = torch.empty(max(1, n * floats), dtype=f32, device=dev)
-            add(f"latent_attention, keys in {splits} run(s) ({tag})", n,
+            add(f"latent_attention, keys in {splits} run(s) ({tag}{', as a portion would run' if per > 1 else ''})", n,
                 timed(lambda: ops.latent_attention_bf16(folded, att, kv, cu, slots, start, n_seqs, per, heads, rank, 0.07, window, splits, runs)),
                 n * heads * (row + rank) * 2 + (n_seqs * (ctx_len + per)) * row * 2, 2 * heads * keys * (row + rank))
+            if per > 1:
+                # a whole prompt: its rows expanded per head by one product, and attention over those
+                w_exp, lat = rnd(heads * (dim + vdim), rank), rnd(n, row)
+                wide = torch.empty(n, heads * (dim + vdim), dtype=bf, device=dev)
+                add(f"linear, the prompt's rows per head ({tag})", n, timed(lambda: ops.linear(lat[:, :rank], w_exp, wide)),
+                    w_exp.numel() * 2 + n * (rank + heads * (dim + vdim)) * 2, 2 * n * heads * (dim + vdim) * rank)
+                add(f"expanded_attention ({tag})", n,
+                    timed(lambda: ops.expanded_attention_bf16(q, wide[:, : heads * dim], lat[:, rank:], wide[:, heads * dim:], hd, cu, n_seqs, per,
+                                                              heads, dim, rot, vdim, 0.07, window)),
+                    n * heads * (2 * dim + rot + 2 * vdim) * 2 + n * rot * 2, 2 * heads * keys * (dim + rot + vdim))
             ql, ml = rnd(n, heads * 128), torch.empty(n, heads * 128, dtype=bf, device=dev)
             if per == 1:
                 splits, chunk, ring = ops.attention_decode_plan(n, heads, heads // 2, 128, ctx_len + 1, 0, n * (ctx_len + 1))

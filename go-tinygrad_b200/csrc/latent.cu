@@ -127,7 +127,7 @@ GTG_API int gtg_latent_prepare(int dtype, void* q, int ldq, const void* dkv, int
 // are bounded), two pages in flight.  Per page, sixteen warps as 2 row
 // groups x 8: first every warp multiplies its 16 query rows with an eighth of
 // the page's 64 keys over all rank + rot channels (S, float), the row maxima and
-// sums meet through shared memory (streaming softmax in float, expf), the
+// sums meet through shared memory (streaming softmax in float, powers of two), the
 // weights go to shared memory as bfloat16; then every warp adds, for its 16
 // rows, an eighth of the value channels: O[16, rank/8] += P[16, 64] . page[64,
 // eighth], the page's first rank columns read transposed (ldmatrix.trans).  O
@@ -168,6 +168,15 @@ __device__ __forceinline__ void bulk_row(uint32_t dst, const void* src, uint32_t
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+
+// 2^x by the special-function unit (the bfloat16 attention kernels of this library all do: scores are
+// scaled by log2(e) so that exponentials are powers of two).  ex2(-inf) = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+constexpr float kLog2e = 1.4426950408889634f;
 
 constexpr int kTileRows = 32;
 constexpr int kLatThreads = 512;
@@ -323,7 +332,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
             const int hh = e >> 1;
             const int key = p * kPageTokens + part_i * 8 + t * 2 + (e & 1);
             const bool seen = pos_r[hh] >= 0 && key <= pos_r[hh] && key >= lo_r[hh];
-            s[e] = seen ? s[e] * scale : -INFINITY;
+            s[e] = seen ? s[e] * (scale * kLog2e) : -INFINITY;
             mx[hh] = fmaxf(mx[hh], s[e]);
         }
 #pragma unroll
@@ -340,10 +349,10 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
             float m_new = m_run[hh];
 #pragma unroll
             for (int qq = 0; qq < kParts; ++qq) m_new = fmaxf(m_new, part[qq * kTileRows + r]);
-            corr[hh] = m_new == -INFINITY ? 1.f : expf(m_run[hh] - m_new);
+            corr[hh] = m_new == -INFINITY ? 1.f : fast_exp2(m_run[hh] - m_new);
             m_run[hh] = m_new;
-            const float p0 = s[hh * 2] == -INFINITY ? 0.f : expf(s[hh * 2] - m_new);
-            const float p1 = s[hh * 2 + 1] == -INFINITY ? 0.f : expf(s[hh * 2 + 1] - m_new);
+            const float p0 = m_new == -INFINITY ? 0.f : fast_exp2(s[hh * 2] - m_new);
+            const float p1 = m_new == -INFINITY ? 0.f : fast_exp2(s[hh * 2 + 1] - m_new);
             const __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
             // the sum runs over the rounded weights, the ones the values are multiplied with
             sum[hh] = __bfloat162float(pr.x) + __bfloat162float(pr.y);
@@ -437,7 +446,7 @@ latent_attention_merge_kernel(const float* __restrict__ scratch, bf16* __restric
     float M = -INFINITY;
     for (int z = 0; z < n_splits; ++z) M = fmaxf(M, ms[z]);
     if (M == -INFINITY) return;
-    if (threadIdx.x < n_splits) ws[threadIdx.x] = ms[threadIdx.x] == -INFINITY ? 0.f : expf(ms[threadIdx.x] - M);
+    if (threadIdx.x < n_splits) ws[threadIdx.x] = ms[threadIdx.x] == -INFINITY ? 0.f : exp2f(ms[threadIdx.x] - M);   // maxima are in powers of two
     __syncthreads();
     float L = 0.f;
     for (int z = 0; z < n_splits; ++z) L = fmaf(ws[z], ls[z], L);
@@ -552,8 +561,9 @@ GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo
 // rows: q [N, heads, dim + rot] (rotated part last, already rotated), kn [N, heads, dim], the
 // shared rotated key part kr [N, rot] (row stride ldr), v [N, heads, vdim] -> out [N, heads,
 // vdim].  One block of four warps per (64 queries, head, sequence); a warp owns 16 query rows
-// with their fragments in registers, walks tiles of 64 keys staged by cp.async (two in flight),
-// S and the streaming softmax (float, expf) stay in its registers, the weights become the
+// with their fragments in registers, walks tiles of 64 keys staged by bulk copies (two in flight;
+// bounded waits as in the kernel above),
+// S and the streaming softmax (float, powers of two) stay in its registers, the weights become the
 // left operand of the value product without leaving them, O stays in registers.  Causal, window
 // as everywhere.  KS = (dim + rot) / 16 and NV = vdim / 8 at most (template), dim and rot
 // multiples of 16, vdim of 8.
@@ -565,7 +575,7 @@ __global__ void __launch_bounds__(kExpThreads)
 expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kn, int ldk,
                           const bf16* __restrict__ kr, int ldr, const bf16* __restrict__ v, int ldv,
                           bf16* __restrict__ out, int ldo, const int* __restrict__ cu_seqlens,
-                          int dim, int rot, int vdim, float scale, int window) {
+                          int dim, int rot, int vdim, float scale, int window, int test_waits) {
     chain_release();
     chain_wait();
     extern __shared__ __align__(128) unsigned char smem[];
@@ -579,8 +589,15 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
     const int ldks = dk + kPad, ldvs = vdim + kPad;             // staged rows, in elements
     bf16* k_s = reinterpret_cast<bf16*>(smem);                  // [2][64][ldks]; the first buffer holds the queries at the start
     bf16* v_s = k_s + 2 * kKTile * ldks;                        // [2][64][ldvs]
+    const uint32_t bars = smem_u32(v_s + 2 * kKTile * ldvs);    // two barriers of 8 bytes: a staged tile has arrived
+    volatile int* gave_up = reinterpret_cast<int*>(v_s + 2 * kKTile * ldvs) + 4;      // set by a thread whose wait ran out
     const int n_ks = dk / 16, n_nv = vdim / 8;
-    const int kc_n = dim / 8, kc_r = rot / 8, vc = vdim / 8;    // 16-byte chunks per row
+    if (tid == 0) {
+        *gave_up = 0;
+        mbar_init(bars, 1);
+        mbar_init(bars + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
+    }
 
     // the queries: staged, then each warp's 16 rows into registers
     for (int r = warp; r < kQTile; r += kExpThreads / 32) {
@@ -603,23 +620,28 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
     const int q_hi = min(q0 + kQTile, len) - 1;
     const int lo_min = (window > 0 && q0 - window + 1 > 0) ? q0 - window + 1 : 0;
     const int t_lo = lo_min / kKTile, t_hi = q_hi / kKTile;
+    // A tile of keys and values is staged by the copy engine, three bulk copies a key (its head's
+    // unrotated part, the shared rotated part, its head's value), issued by warp 0 and counted on the
+    // tile's barrier: the warps that multiply issue no copy.  Value rows past the sequence's end are
+    // zeroed by hand (their weights are zero, but zero times a stale NaN is not).
     auto load_tile = [&](int buf, int kt) {
         bf16* kd = k_s + (size_t)buf * kKTile * ldks;
         bf16* vd = v_s + (size_t)buf * kKTile * ldvs;
-        for (int r = warp; r < kKTile; r += kExpThreads / 32) {
-            const int key = kt * kKTile + r;
-            const bool ok = key < len;
-            const size_t row = (size_t)(tok0 + (ok ? key : 0));
-            const bf16* sn = kn + row * ldk + (size_t)h * dim;
-            const bf16* sr = kr + row * ldr;
-            const bf16* sv = v + row * ldv + (size_t)h * vdim;
-            for (int c = lane; c < kc_n; c += 32) cp_async16(smem_u32(kd + r * ldks + c * 8), sn + c * 8, ok ? 16 : 0);
-            for (int c = lane; c < kc_r; c += 32) cp_async16(smem_u32(kd + r * ldks + dim + c * 8), sr + c * 8, ok ? 16 : 0);
-            for (int c = lane; c < vc; c += 32) cp_async16(smem_u32(vd + r * ldvs + c * 8), sv + c * 8, ok ? 16 : 0);
+        const int valid = min(kKTile, len - kt * kKTile);
+        for (int idx = valid * (vdim / 2) + tid; idx < kKTile * (vdim / 2); idx += kExpThreads)
+            reinterpret_cast<uint32_t*>(vd + (idx / (vdim / 2)) * ldvs)[idx % (vdim / 2)] = 0u;
+        if (warp != 0) return;
+        if (lane == 0) mbar_expect_tx(bars + 8 * buf, (uint32_t)(valid * (dk + vdim) * 2));
+        __syncwarp();
+        if (test_waits) return;
+        for (int r = lane; r < valid; r += 32) {
+            const size_t row = (size_t)(tok0 + kt * kKTile + r);
+            bulk_row(smem_u32(kd + r * ldks), kn + row * ldk + (size_t)h * dim, (uint32_t)(dim * 2), bars + 8 * buf);
+            bulk_row(smem_u32(kd + r * ldks + dim), kr + row * ldr, (uint32_t)(rot * 2), bars + 8 * buf);
+            bulk_row(smem_u32(vd + r * ldvs), v + row * ldv + (size_t)h * vdim, (uint32_t)(vdim * 2), bars + 8 * buf);
         }
     };
     load_tile(0, t_lo);
-    cp_async_commit();
 
     float o[NV][4];
 #pragma unroll
@@ -637,11 +659,10 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
 
     for (int kt = t_lo; kt <= t_hi; ++kt) {
         const int buf = (kt - t_lo) & 1;
-        if (kt > t_lo) __syncthreads();                         // everyone is done with the tile before
+        __syncthreads();                                        // everyone is done with the tile before (and sees the zeroed rows)
+        if (*gave_up) break;                                    // a wait ran out: no barrier is armed again (see the kernel above)
         if (kt + 1 <= t_hi) load_tile(buf ^ 1, kt + 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();                                        // tile kt staged
+        if (!mbar_wait(bars + 8 * buf, ((uint32_t)(kt - t_lo) >> 1) & 1u, test_waits ? 1024u : kPageWaitLimit)) *gave_up = 1;
         const bf16* kd = k_s + (size_t)buf * kKTile * ldks;
         const bf16* vd = v_s + (size_t)buf * kKTile * ldvs;
         float s[8][4];
@@ -674,7 +695,7 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
                 const int hh = e >> 1;
                 const int key = kt * kKTile + j * 8 + t * 2 + (e & 1);
                 const bool seen = pos_r[hh] >= 0 && key <= pos_r[hh] && key >= lo_r[hh];
-                s[j][e] = seen ? s[j][e] * scale : -INFINITY;
+                s[j][e] = seen ? s[j][e] * (scale * kLog2e) : -INFINITY;
                 mx[hh] = fmaxf(mx[hh], s[j][e]);
             }
         float corr[2], sum[2] = {0.f, 0.f};
@@ -683,7 +704,7 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
             mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
             mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
             const float m_new = fmaxf(m_run[hh], mx[hh]);
-            corr[hh] = m_new == -INFINITY ? 1.f : expf(m_run[hh] - m_new);
+            corr[hh] = m_new == -INFINITY ? 1.f : fast_exp2(m_run[hh] - m_new);
             m_run[hh] = m_new;
         }
         uint32_t pf[4][4];                                      // the weights as left operand: 4 steps of 16 keys
@@ -691,7 +712,7 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
         for (int j = 0; j < 8; ++j) {
             float p[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) p[e] = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - m_run[e >> 1]);
+            for (int e = 0; e < 4; ++e) p[e] = m_run[e >> 1] == -INFINITY ? 0.f : fast_exp2(s[j][e] - m_run[e >> 1]);
             const __nv_bfloat162 lo = __floats2bfloat162_rn(p[0], p[1]), hi = __floats2bfloat162_rn(p[2], p[3]);
             // the sums run over the rounded weights, the ones the values are multiplied with
             sum[0] += __bfloat162float(lo.x) + __bfloat162float(lo.y);
@@ -730,7 +751,6 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
             }
         }
     }
-    cp_async_wait<0>();
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         if (pos_r[hh] < 0 || l_run[hh] <= 0.f) continue;
@@ -744,7 +764,7 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
 }
 
 size_t expanded_attention_smem(int dk, int vdim) {
-    return (size_t)2 * kKTile * ((dk + kPad) + (vdim + kPad)) * 2;
+    return (size_t)2 * kKTile * ((dk + kPad) + (vdim + kPad)) * 2 + 32;
 }
 }  // namespace
 
@@ -777,7 +797,7 @@ GTG_API int gtg_expanded_attention_bf16(const void* q, int ldq, const void* kn, 
         }                                                                                                           \
         return launch_chained(expanded_attention_kernel<KS, NV>, grid, dim3(kExpThreads), smem, stream, (const bf16*)q, ldq, \
                               (const bf16*)kn, ldk, (const bf16*)kr, ldr, (const bf16*)v, ldv, (bf16*)out, ldo, cu_seqlens, \
-                              dim, rot, vdim, scale, window);                                                       \
+                              dim, rot, vdim, scale, window, g_latent_test_waits ? 1 : 0);                         \
     } while (0)
     const int ks = (dim + rot) / 16;
     if (vdim <= 64) {

@@ -87,6 +87,30 @@ def latent_attention():
     return run, want, dict(rtol=2e-2, atol=2e-2)
 
 
+def expanded_attention():
+    """Attention of whole prompts over keys and values per head (the other kernel of the same library)."""
+    heads, dim, rot, vdim, lens = 3, 32, 16, 24, [150, 70]
+    n, dk = sum(lens), dim + rot
+    q = rnd(n, heads * dk, dtype=BF16, seed=1, scale=0.5)
+    kn, kr, v = rnd(n, heads * dim, dtype=BF16, seed=2), rnd(n, rot, dtype=BF16, seed=3), rnd(n, heads * vdim, dtype=BF16, seed=4)
+    cu = torch.tensor([0, lens[0], n], dtype=torch.int32, device=DEV)
+    want, at = [], 0
+    for L in lens:
+        for i in range(L):
+            keys = slice(at, at + i + 1)
+            sc = (torch.einsum("hd,khd->hk", q[at + i].double().view(heads, dk)[:, :dim], kn[keys].double().view(-1, heads, dim))
+                  + q[at + i].double().view(heads, dk)[:, dim:] @ kr[keys].double().T) * 0.15
+            want.append(torch.einsum("hk,khd->hd", torch.softmax(sc, dim=-1), v[keys].double().view(-1, heads, vdim)).reshape(-1))
+        at += L
+    want = torch.stack(want).float()
+
+    def run():
+        out = torch.full((n, heads * vdim), 7.0, dtype=BF16, device=DEV)
+        ops.expanded_attention_bf16(q, kn, kr, v, out, cu, 2, max(lens), heads, dim, rot, vdim, 0.15, 0)
+        return out.float()
+    return run, want, dict(rtol=2e-2, atol=2e-2)
+
+
 CASES = {
     # library -> what runs its kernels: (how to build the case)
     "gemm_bf16_tcgen05": [lambda: product("tcgen05", 300, 520, 1024), residual_product],
@@ -97,7 +121,7 @@ CASES = {
                          lambda: product("skinny", 3, 50, 8200),         # an inner size that takes the row-copy kernel,
                          lambda: product("skinny", 5, 96, 264)],         # ... with a cluster of ranks and with one
     "attention_tcgen05": [prompt_attention],
-    "latent": [latent_attention],
+    "latent": [latent_attention, expanded_attention],
 }
 
 
