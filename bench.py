@@ -656,14 +656,15 @@ def run_design(args):
                 n * heads * (row + rank) * 2 + (n_seqs * (ctx_len + per)) * row * 2, 2 * heads * keys * (row + rank))
             if per > 1:
                 # a whole prompt: its rows expanded per head by one product, and attention over those
-                w_exp, lat = rnd(heads * (dim + vdim), rank), rnd(n, row)
-                wide = torch.empty(n, heads * (dim + vdim), dtype=bf, device=dev)
-                add(f"linear, the prompt's rows per head ({tag})", n, timed(lambda: ops.linear(lat[:, :rank], w_exp, wide)),
-                    w_exp.numel() * 2 + n * (rank + heads * (dim + vdim)) * 2, 2 * n * heads * (dim + vdim) * rank)
+                per_head = dim + vdim + rot
+                w_exp, lat = rnd(heads * per_head, rank), rnd(n, row)
+                runs = torch.empty(n, heads * per_head, dtype=bf, device=dev)
+                add(f"linear, the prompt's rows per head ({tag})", n, timed(lambda: ops.linear(lat[:, :rank], w_exp, runs)),
+                    w_exp.numel() * 2 + n * (rank + heads * per_head) * 2, 2 * n * heads * per_head * rank)
+                add(f"latent_spread ({tag})", n, timed(lambda: ops.latent_spread(lat[:, rank:], runs, heads, dim + vdim)), n * (heads + 1) * rot * 2)
                 add(f"expanded_attention ({tag})", n,
-                    timed(lambda: ops.expanded_attention_bf16(q, wide[:, : heads * dim], lat[:, rank:], wide[:, heads * dim:], hd, cu, n_seqs, per,
-                                                              heads, dim, rot, vdim, 0.07, window)),
-                    n * heads * (2 * dim + rot + 2 * vdim) * 2 + n * rot * 2, 2 * heads * keys * (dim + rot + vdim))
+                    timed(lambda: ops.expanded_attention_bf16(q, runs, hd, cu, n_seqs, per, heads, dim, rot, vdim, 0.07, window)),
+                    n * heads * (dim + rot + per_head + vdim) * 2, 2 * heads * keys * (dim + rot + vdim))
             ql, ml = rnd(n, heads * 128), torch.empty(n, heads * 128, dtype=bf, device=dev)
             if per == 1:
                 splits, chunk, ring = ops.attention_decode_plan(n, heads, heads // 2, 128, ctx_len + 1, 0, n * (ctx_len + 1))

@@ -558,22 +558,23 @@ GTG_API int gtg_latent_attention_bf16(const void* q, int ldq, void* out, int ldo
 // there are, and expanding them per head (K_h = U_h c, V_h = V_h c: two products over the step's
 // latents) costs less than attending in the folded form: dim + rot channels per score and vdim
 // per value instead of rank + rot and rank.  This kernel is the attention over those expanded
-// rows: q [N, heads, dim + rot] (rotated part last, already rotated), kn [N, heads, dim], the
-// shared rotated key part kr [N, rot] (row stride ldr), v [N, heads, vdim] -> out [N, heads,
-// vdim].  One block of four warps per (64 queries, head, sequence); a warp owns 16 query rows
-// with their fragments in registers, walks tiles of 64 keys staged by bulk copies (two in flight;
+// rows: q [N, heads, dim + rot] (rotated part last, already rotated), and per token and head one
+// run kv [N, heads, dim + vdim + rot] = [U_h c | V_h c | k'] (the product leaves the rotated key
+// part's place empty and `latent_spread` copies it in for every head, so that a key is one bulk
+// copy: what costs in staging is the number of copies, not their bytes) -> out [N, heads, vdim].  One block of eight warps per (128 queries, head, sequence); a warp owns 16 query rows
+// with their fragments in registers, walks tiles of 64 keys staged by bulk copies (three in flight;
 // bounded waits as in the kernel above),
 // S and the streaming softmax (float, powers of two) stay in its registers, the weights become the
 // left operand of the value product without leaving them, O stays in registers.  Causal, window
 // as everywhere.  KS = (dim + rot) / 16 and NV = vdim / 8 at most (template), dim and rot
 // multiples of 16, vdim of 8.
 namespace {
-constexpr int kQTile = 64, kKTile = 64, kExpThreads = 128;
+constexpr int kQTile = 128, kKTile = 64, kExpThreads = 256;
+constexpr int kStages = 4;           // tiles of keys and values in flight: a tile's copies take several tiles' worth of arithmetic to land
 
 template <int KS, int NV>
 __global__ void __launch_bounds__(kExpThreads)
-expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kn, int ldk,
-                          const bf16* __restrict__ kr, int ldr, const bf16* __restrict__ v, int ldv,
+expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kv, int ldkv,
                           bf16* __restrict__ out, int ldo, const int* __restrict__ cu_seqlens,
                           int dim, int rot, int vdim, float scale, int window, int test_waits) {
     chain_release();
@@ -586,16 +587,16 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int dk = dim + rot;
-    const int ldks = dk + kPad, ldvs = vdim + kPad;             // staged rows, in elements
-    bf16* k_s = reinterpret_cast<bf16*>(smem);                  // [2][64][ldks]; the first buffer holds the queries at the start
-    bf16* v_s = k_s + 2 * kKTile * ldks;                        // [2][64][ldvs]
-    const uint32_t bars = smem_u32(v_s + 2 * kKTile * ldvs);    // two barriers of 8 bytes: a staged tile has arrived
-    volatile int* gave_up = reinterpret_cast<int*>(v_s + 2 * kKTile * ldvs) + 4;      // set by a thread whose wait ran out
+    const int per = dim + vdim + rot;                           // a key's run: [unrotated key | value | rotated key part]
+    const int ldks = dk + kPad, ldt = per + kPad;               // staged rows, in elements
+    bf16* k_s = reinterpret_cast<bf16*>(smem);                  // the queries at the start [128][ldks], then
+    bf16* t_s = k_s;                                            // [stages][64][ldt]: the tiles of keys and values
+    const uint32_t bars = smem_u32(t_s + kStages * kKTile * ldt);     // a barrier of 8 bytes per stage: a staged tile has arrived
+    volatile int* gave_up = reinterpret_cast<int*>(t_s + kStages * kKTile * ldt) + 2 * kStages;       // set by a thread whose wait ran out
     const int n_ks = dk / 16, n_nv = vdim / 8;
     if (tid == 0) {
         *gave_up = 0;
-        mbar_init(bars, 1);
-        mbar_init(bars + 8, 1);
+        for (int st = 0; st < kStages; ++st) mbar_init(bars + 8 * st, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
     }
 
@@ -620,28 +621,23 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
     const int q_hi = min(q0 + kQTile, len) - 1;
     const int lo_min = (window > 0 && q0 - window + 1 > 0) ? q0 - window + 1 : 0;
     const int t_lo = lo_min / kKTile, t_hi = q_hi / kKTile;
-    // A tile of keys and values is staged by the copy engine, three bulk copies a key (its head's
-    // unrotated part, the shared rotated part, its head's value), issued by warp 0 and counted on the
-    // tile's barrier: the warps that multiply issue no copy.  Value rows past the sequence's end are
-    // zeroed by hand (their weights are zero, but zero times a stale NaN is not).
+    // A tile of keys and values is staged by the copy engine, one bulk copy a key, issued by warp 0 and
+    // counted on the tile's barrier: the warps that multiply issue no copy.  Value rows past the
+    // sequence's end are zeroed by hand (their weights are zero, but zero times a stale NaN is not).
     auto load_tile = [&](int buf, int kt) {
-        bf16* kd = k_s + (size_t)buf * kKTile * ldks;
-        bf16* vd = v_s + (size_t)buf * kKTile * ldvs;
+        bf16* td = t_s + (size_t)buf * kKTile * ldt;
         const int valid = min(kKTile, len - kt * kKTile);
         for (int idx = valid * (vdim / 2) + tid; idx < kKTile * (vdim / 2); idx += kExpThreads)
-            reinterpret_cast<uint32_t*>(vd + (idx / (vdim / 2)) * ldvs)[idx % (vdim / 2)] = 0u;
+            reinterpret_cast<uint32_t*>(td + (idx / (vdim / 2)) * ldt + dim)[idx % (vdim / 2)] = 0u;
         if (warp != 0) return;
-        if (lane == 0) mbar_expect_tx(bars + 8 * buf, (uint32_t)(valid * (dk + vdim) * 2));
+        if (lane == 0) mbar_expect_tx(bars + 8 * buf, (uint32_t)(valid * per * 2));
         __syncwarp();
         if (test_waits) return;
-        for (int r = lane; r < valid; r += 32) {
-            const size_t row = (size_t)(tok0 + kt * kKTile + r);
-            bulk_row(smem_u32(kd + r * ldks), kn + row * ldk + (size_t)h * dim, (uint32_t)(dim * 2), bars + 8 * buf);
-            bulk_row(smem_u32(kd + r * ldks + dim), kr + row * ldr, (uint32_t)(rot * 2), bars + 8 * buf);
-            bulk_row(smem_u32(vd + r * ldvs), v + row * ldv + (size_t)h * vdim, (uint32_t)(vdim * 2), bars + 8 * buf);
-        }
+        for (int r = lane; r < valid; r += 32)
+            bulk_row(smem_u32(td + r * ldt), kv + (size_t)(tok0 + kt * kKTile + r) * ldkv + (size_t)h * per, (uint32_t)(per * 2), bars + 8 * buf);
     };
-    load_tile(0, t_lo);
+    for (int st = 0; st < kStages - 1; ++st)
+        if (t_lo + st <= t_hi) load_tile(st, t_lo + st);
 
     float o[NV][4];
 #pragma unroll
@@ -658,27 +654,27 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
     }
 
     for (int kt = t_lo; kt <= t_hi; ++kt) {
-        const int buf = (kt - t_lo) & 1;
+        const int buf = (kt - t_lo) % kStages;
         __syncthreads();                                        // everyone is done with the tile before (and sees the zeroed rows)
         if (*gave_up) break;                                    // a wait ran out: no barrier is armed again (see the kernel above)
-        if (kt + 1 <= t_hi) load_tile(buf ^ 1, kt + 1);
-        if (!mbar_wait(bars + 8 * buf, ((uint32_t)(kt - t_lo) >> 1) & 1u, test_waits ? 1024u : kPageWaitLimit)) *gave_up = 1;
-        const bf16* kd = k_s + (size_t)buf * kKTile * ldks;
-        const bf16* vd = v_s + (size_t)buf * kKTile * ldvs;
+        if (kt + kStages - 1 <= t_hi) load_tile((kt + kStages - 1 - t_lo) % kStages, kt + kStages - 1);   // into the buffer of the tile before
+        if (!mbar_wait(bars + 8 * buf, ((uint32_t)(kt - t_lo) / kStages) & 1u, test_waits ? 1024u : kPageWaitLimit)) *gave_up = 1;
+        const bf16* td = t_s + (size_t)buf * kKTile * ldt;
         float s[8][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
         {
-            const uint32_t b_addr = smem_u32(kd + ((lane & 7) + (lane >> 4) * 8) * ldks + ((lane >> 3) & 1) * 8);
+            const uint32_t b_addr = smem_u32(td + ((lane & 7) + (lane >> 4) * 8) * ldt + ((lane >> 3) & 1) * 8);
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
                 if (ks < n_ks) {
                     uint32_t bfr[4][4];
 #pragma unroll
                     for (int jj = 0; jj < 4; ++jj)
-                        ldmatrix_x4(bfr[jj][0], bfr[jj][1], bfr[jj][2], bfr[jj][3], b_addr + (jj * 16 * ldks + ks * 16) * 2);
+                        // channel step ks: the unrotated key's channels first, the rotated part's behind the value
+                        ldmatrix_x4(bfr[jj][0], bfr[jj][1], bfr[jj][2], bfr[jj][3], b_addr + (jj * 16 * ldt + (ks * 16 < dim ? ks * 16 : vdim + ks * 16)) * 2);
 #pragma unroll
                     for (int jj = 0; jj < 4; ++jj) {
                         mma_bf16_16816(s[2 * jj], qf[ks], bfr[jj][0], bfr[jj][1]);
@@ -731,7 +727,7 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
             o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
         }
         {
-            const uint32_t v_addr = smem_u32(vd + ((lane & 7) + ((lane >> 3) & 1) * 8) * ldvs + (lane >> 4) * 8);
+            const uint32_t v_addr = smem_u32(td + ((lane & 7) + ((lane >> 3) & 1) * 8) * ldt + dim + (lane >> 4) * 8);
 #pragma unroll
             for (int ks = 0; ks < kKTile / 16; ++ks) {
 #pragma unroll
@@ -740,7 +736,7 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
 #pragma unroll
                     for (int j = 0; j < 8; j += 2)
                         if (c + j < n_nv)
-                            ldmatrix_x4_trans(vf[j / 2][0], vf[j / 2][1], vf[j / 2][2], vf[j / 2][3], v_addr + (ks * 16 * ldvs + (c + j) * 8) * 2);
+                            ldmatrix_x4_trans(vf[j / 2][0], vf[j / 2][1], vf[j / 2][2], vf[j / 2][3], v_addr + (ks * 16 * ldt + (c + j) * 8) * 2);
 #pragma unroll
                     for (int j = 0; j < 8; j += 2)
                         if (c + j < n_nv) {
@@ -764,7 +760,21 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
 }
 
 size_t expanded_attention_smem(int dk, int vdim) {
-    return (size_t)2 * kKTile * ((dk + kPad) + (vdim + kPad)) * 2 + 32;
+    const size_t tiles = (size_t)kStages * kKTile * (dk + vdim + kPad) * 2, queries = (size_t)kQTile * (dk + kPad) * 2;
+    return (tiles > queries ? tiles : queries) + 8 * kStages + 16;
+}
+
+// kv[n, h, dim + vdim : dim + vdim + rot] = kr[n, :] for every head: the shared rotated key part into its place in every head's run.
+__global__ void latent_spread_kernel(const bf16* __restrict__ kr, int ldr, bf16* __restrict__ kv, int ldkv, int n_heads, int per,
+                                     int offset, int rot8) {
+    chain_release();
+    chain_wait();
+    const int n = blockIdx.x;
+    for (int idx = threadIdx.x; idx < n_heads * rot8; idx += blockDim.x) {
+        const int h = idx / rot8, c = idx % rot8;
+        *reinterpret_cast<uint4*>(kv + (size_t)n * ldkv + (size_t)h * per + offset + c * 8) =
+            *reinterpret_cast<const uint4*>(kr + (size_t)n * ldr + c * 8);
+    }
 }
 }  // namespace
 
@@ -773,16 +783,24 @@ GTG_API int gtg_expanded_attention_supports(int dim, int rot, int vdim) {
 }
 
 // Attention of a step whose sequences all start at their first token, over the step's own rows expanded per head.
-GTG_API int gtg_expanded_attention_bf16(const void* q, int ldq, const void* kn, int ldk, const void* kr, int ldr,
-                                        const void* v, int ldv, void* out, int ldo, const int* cu_seqlens, int n_seqs,
+// kv[n, h, offset : offset + rot] = kr[n, 0 : rot] for every head h (runs of `per` channels a head; all multiples of 8).
+GTG_API int gtg_latent_spread(const void* kr, int ldr, void* kv, int ldkv, int N, int n_heads, int per, int offset, int rot,
+                              cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (n_heads <= 0 || rot <= 0 || offset < 0 || offset + rot > per) return kErrBadArgument;
+    if (rot % 8 || per % 8 || offset % 8 || ldr % 8 || ldkv % 8 || ((uintptr_t)kr % 16) || ((uintptr_t)kv % 16)) return kErrUnsupported;
+    return launch_chained(latent_spread_kernel, dim3(N), dim3(128), 0, stream, (const bf16*)kr, ldr, (bf16*)kv, ldkv, n_heads, per,
+                          offset, rot / 8);
+}
+
+GTG_API int gtg_expanded_attention_bf16(const void* q, int ldq, const void* kv, int ldkv,
+                                        void* out, int ldo, const int* cu_seqlens, int n_seqs,
                                         int max_q_len, int n_heads, int dim, int rot, int vdim, float scale, int window,
                                         cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (n_heads <= 0) return kErrBadArgument;
     if (!gtg_expanded_attention_supports(dim, rot, vdim)) return kErrUnsupported;
-    if (ldq % 8 || ldk % 8 || ldr % 8 || ldv % 8 || ldo % 2 || ((uintptr_t)q % 16) || ((uintptr_t)kn % 16) || ((uintptr_t)kr % 16) ||
-        ((uintptr_t)v % 16) || ((uintptr_t)out % 4))
-        return kErrUnsupported;
+    if (ldq % 8 || ldkv % 8 || ldo % 2 || ((uintptr_t)q % 16) || ((uintptr_t)kv % 16) || ((uintptr_t)out % 4)) return kErrUnsupported;
     if (n_heads > 65535 || n_seqs > 65535) return kErrUnsupported;
     const size_t smem = expanded_attention_smem(dim + rot, vdim);
     const dim3 grid((max_q_len + kQTile - 1) / kQTile, n_heads, n_seqs);
@@ -791,12 +809,12 @@ GTG_API int gtg_expanded_attention_bf16(const void* q, int ldq, const void* kn, 
         static bool configured = false;                                                                             \
         if (!configured) {                                                                                          \
             const cudaError_t e = cudaFuncSetAttribute(expanded_attention_kernel<KS, NV>,                           \
-                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);    \
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);    \
             if (e != cudaSuccess) return (int)e;                                                                    \
             configured = true;                                                                                      \
         }                                                                                                           \
         return launch_chained(expanded_attention_kernel<KS, NV>, grid, dim3(kExpThreads), smem, stream, (const bf16*)q, ldq, \
-                              (const bf16*)kn, ldk, (const bf16*)kr, ldr, (const bf16*)v, ldv, (bf16*)out, ldo, cu_seqlens, \
+                              (const bf16*)kv, ldkv, (bf16*)out, ldo, cu_seqlens,                                  \
                               dim, rot, vdim, scale, window, g_latent_test_waits ? 1 : 0);                         \
     } while (0)
     const int ks = (dim + rot) / 16;

@@ -67,7 +67,8 @@ _SIGNATURES = {
     "gtg_latent_prepare": ("latent", [_I, _P, _I, _P, _I, _P, _P, _F, _P, _L, _P, _I, _P, _P, _P, _P, _I,
                                       _I, _I, _I, _I, _I, _I, _P, _I, _P]),
     "gtg_expanded_attention_supports": ("latent", [_I, _I, _I]),
-    "gtg_expanded_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]),
+    "gtg_expanded_attention_bf16": ("latent", [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]),
+    "gtg_latent_spread": ("latent", [_P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
     "gtg_latent_attention_supports": ("latent", [_I, _I]),
     "gtg_latent_status": ("latent", []),
     "gtg_latent_test_hooks": ("latent", [_I]),
@@ -1042,27 +1043,35 @@ def expanded_attention_supports(dim: int, rot: int, v_dim: int) -> bool:
     return bool(_fn("gtg_expanded_attention_supports")(int(dim), int(rot), int(v_dim)))
 
 
-def expanded_attention_bf16(q: torch.Tensor, k_plain: torch.Tensor, k_rot: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
-                            cu_seqlens, n_seqs: int, max_q_len: int, n_heads: int, dim: int, rot: int, v_dim: int,
-                            scale: float, window: int = 0) -> None:
+def latent_spread(k_rot: torch.Tensor, runs: torch.Tensor, n_heads: int, offset: int) -> None:
+    """runs[n, h, offset : offset + rot] = k_rot[n, :] for every head: the one rotated key
+    part of a token into its place in every head's run (runs [N, heads * per], bfloat16)."""
+    _rows2d(k_rot, "latent_spread: k_rot"); _rows2d(runs, "latent_spread: runs")
+    N, rot = k_rot.shape
+    _need(runs.shape[0] == N and runs.shape[1] % n_heads == 0 and k_rot.dtype == torch.bfloat16 and runs.dtype == torch.bfloat16,
+          "latent_spread: bfloat16 k_rot [N, rot] and runs [N, heads * per]")
+    _check(_fn("gtg_latent_spread")(_ptr(k_rot), k_rot.stride(0), _ptr(runs), runs.stride(0), N, n_heads, runs.shape[1] // n_heads,
+                                    int(offset), rot, _stream()), "latent_spread")
+
+
+def expanded_attention_bf16(q: torch.Tensor, runs: torch.Tensor, out: torch.Tensor, cu_seqlens, n_seqs: int, max_q_len: int,
+                            n_heads: int, dim: int, rot: int, v_dim: int, scale: float, window: int = 0) -> None:
     """Attention of a step whose sequences all start at their first token, over the
     step's own rows with keys and values per head: q [N, heads * (dim + rot)] (a
-    head's rotated part last, rotated), k_plain [N, heads * dim], k_rot [N, rot]
-    (one rotated key part for all heads), v [N, heads * v_dim] -> out [N, heads *
+    head's rotated part last, rotated); runs [N, heads * (dim + v_dim + rot)], per
+    token and head [unrotated key | value | rotated key part] -> out [N, heads *
     v_dim].  Causal within each sequence, over the last `window` keys (0: all)."""
-    for name, t in (("q", q), ("k_plain", k_plain), ("k_rot", k_rot), ("v", v), ("out", out)):
+    for name, t in (("q", q), ("runs", runs), ("out", out)):
         _rows2d(t, f"expanded_attention: {name}")
         _need(t.dtype == torch.bfloat16, "expanded_attention_bf16: bfloat16 only")
     N = q.shape[0]
-    _need(q.shape[1] == n_heads * (dim + rot) and tuple(k_plain.shape) == (N, n_heads * dim) and tuple(k_rot.shape) == (N, rot)
-          and tuple(v.shape) == (N, n_heads * v_dim) and tuple(out.shape) == (N, n_heads * v_dim),
-          "expanded_attention_bf16: shapes do not agree")
+    _need(q.shape[1] == n_heads * (dim + rot) and tuple(runs.shape) == (N, n_heads * (dim + v_dim + rot))
+          and tuple(out.shape) == (N, n_heads * v_dim), "expanded_attention_bf16: shapes do not agree")
     _need(expanded_attention_supports(dim, rot, v_dim), "expanded_attention_bf16: head sizes not supported")
     _int32("expanded_attention_bf16", cu_seqlens)
-    _check(_fn("gtg_expanded_attention_bf16")(_ptr(q), q.stride(0), _ptr(k_plain), k_plain.stride(0), _ptr(k_rot), k_rot.stride(0),
-                                              _ptr(v), v.stride(0), _ptr(out), out.stride(0), _ptr(cu_seqlens), int(n_seqs),
-                                              int(max_q_len), n_heads, dim, rot, v_dim, float(scale), int(window), _stream()),
-           "expanded_attention_bf16")
+    _check(_fn("gtg_expanded_attention_bf16")(_ptr(q), q.stride(0), _ptr(runs), runs.stride(0), _ptr(out), out.stride(0),
+                                              _ptr(cu_seqlens), int(n_seqs), int(max_q_len), n_heads, dim, rot, v_dim, float(scale),
+                                              int(window), _stream()), "expanded_attention_bf16")
 
 
 # ------------------------------------------------------------------ routed experts

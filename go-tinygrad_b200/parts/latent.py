@@ -110,10 +110,14 @@ class LatentAttention(Mixer):
         # U_h^T per head, [H, rank, dim]: the product that folds U_h into the query reads it as its weight
         self.w_uk_t = rt.matrix(tensors[self.names["uk"]].to(rt.dtype).reshape(H, self.dim, self.rank).transpose(1, 2))
         self.w_uv = rt.matrix(tensors[self.names["uv"]]).view(H, self.v_dim, self.rank)
-        # [U; V] for all heads, [H * (dim + v_dim), rank]: the product that expands a prompt's rows per head
+        # per head [U_h; V_h; rot_dim rows of zeros], [H * (dim + v_dim + rot_dim), rank]: the product that expands a
+        # prompt's rows into one run per token and head, with room for the rotated key part behind key and value
         self.w_expand = None
         if rt.dtype == torch.bfloat16:
-            self.w_expand = rt.matrix(torch.cat([tensors[self.names["uk"]].to(rt.dtype), tensors[self.names["uv"]].to(rt.dtype)], dim=0))
+            uk = tensors[self.names["uk"]].to(rt.dtype).reshape(H, self.dim, self.rank)
+            uv = tensors[self.names["uv"]].to(rt.dtype).reshape(H, self.v_dim, self.rank)
+            room = torch.zeros(H, self.rot, self.rank, dtype=rt.dtype, device=uk.device)   # tensors come from a file or, random, from the device
+            self.w_expand = rt.matrix(torch.cat([uk, uv, room], dim=1).reshape(-1, self.rank))
         self.w_o = rt.matrix(tensors[self.names["o"]])
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheHandle) -> torch.Tensor:
@@ -164,7 +168,7 @@ class LatentAttention(Mixer):
         for a layer without a down projection, the rows the owning layer left in this step."""
         return (ctx.rt.dtype == torch.bfloat16 and not ctx.is_decode
                 and ctx.total_kv_len == ctx.n_tokens and self.rank % 8 == 0 and self.row % 8 == 0
-                and (self.n_heads * self.dim) % 8 == 0 and (self.n_heads * self.v_dim) % 8 == 0
+                and (self.n_heads * self.v_dim) % 8 == 0
                 and ops.expanded_attention_supports(self.dim, self.rot, self.v_dim)
                 and ((self.own_kv and cache.writes) or self._rows_key(cache) in ctx.shared))
 
@@ -180,12 +184,12 @@ class LatentAttention(Mixer):
             rows = ctx.shared[self._rows_key(cache)]
             ops.latent_prepare(q, None, rotation, None, self.eps, None, ctx.token_seq, ctx.slots, ctx.positions,
                                None, H, self.dim, self.rot, self.rank)
-        expanded = rt.empty(n, H * (self.dim + self.v_dim))
-        ops.linear(rows[:, : self.rank], self.w_expand, expanded)
+        runs = rt.empty(n, H * (self.dim + self.v_dim + self.rot))
+        ops.linear(rows[:, : self.rank], self.w_expand, runs)
+        ops.latent_spread(rows[:, self.rank:], runs, H, self.dim + self.v_dim)
         heads = rt.empty(n, H * self.v_dim)
-        ops.expanded_attention_bf16(q, expanded[:, : H * self.dim], rows[:, self.rank:], expanded[:, H * self.dim:], heads,
-                                    ctx.cu_seqlens, ctx.n_seqs, ctx.max_q_len, H, self.dim, self.rot, self.v_dim,
-                                    self.scale, self.window or 0)
+        ops.expanded_attention_bf16(q, runs, heads, ctx.cu_seqlens, ctx.n_seqs, ctx.max_q_len, H, self.dim, self.rot,
+                                    self.v_dim, self.scale, self.window or 0)
         if gate is not None:
             ops.sigmoid_gate(heads, gate)
         return emit_update(heads, self.w_o, ctx)

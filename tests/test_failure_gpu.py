@@ -104,9 +104,11 @@ def expanded_attention():
         at += L
     want = torch.stack(want).float()
 
+    runs = torch.cat([kn.view(n, heads, dim), v.view(n, heads, vdim), kr[:, None, :].expand(n, heads, rot)], dim=2).reshape(n, -1).contiguous()
+
     def run():
         out = torch.full((n, heads * vdim), 7.0, dtype=BF16, device=DEV)
-        ops.expanded_attention_bf16(q, kn, kr, v, out, cu, 2, max(lens), heads, dim, rot, vdim, 0.15, 0)
+        ops.expanded_attention_bf16(q, runs, out, cu, 2, max(lens), heads, dim, rot, vdim, 0.15, 0)
         return out.float()
     return run, want, dict(rtol=2e-2, atol=2e-2)
 

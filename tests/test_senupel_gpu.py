@@ -307,22 +307,26 @@ def test_tensor_core_attention_over_latent_rows(heads, row, rank, window):
 @pytest.mark.parametrize("window", [0, 1, 70, 64])
 def test_attention_over_a_prompt_expanded_per_head(heads, dim, rot, vdim, window):
     """The bfloat16 kernel for steps whose sequences all start at their first token: keys
-    and values per head, one rotated key part for all heads; sequences of 150, 37, 2, 1
-    and 65 tokens in one batch; against softmax in float64."""
+    and values per head in one run with the rotated key part, which a kernel copies in for
+    all heads; sequences of 150, 37, 2, 1 and 65 tokens in one batch; against softmax in float64."""
     rng = np.random.default_rng(heads + dim)
     lens = [150, 37, 2, 1, 65]
     n, dk = sum(lens), dim + rot
     rt = Runtime(DEV, torch.bfloat16)
     ctx = context(rt, lens, [0] * len(lens), list(range(len(lens))))
     q = t32(rng.standard_normal((n, heads * dk)) * 0.5).to(torch.bfloat16)
-    wide = t32(rng.standard_normal((n, heads * (dim + vdim)))).to(torch.bfloat16)     # keys and values side by side, as the mixer has them
+    runs = t32(rng.standard_normal((n, heads, dim + vdim + rot))).to(torch.bfloat16)   # per token and head [key | value | room]
     rows = t32(rng.standard_normal((n, 24 + rot))).to(torch.bfloat16)                  # the rotated key part behind 24 other channels
-    kn, v, kr = wide[:, : heads * dim], wide[:, heads * dim:], rows[:, 24:]
+    kr = rows[:, 24:]
+    runs = runs.reshape(n, heads * (dim + vdim + rot))
+    ops.latent_spread(kr, runs, heads, dim + vdim)
+    assert torch.equal(runs.view(n, heads, -1)[:, :, dim + vdim:], kr[:, None, :].expand(n, heads, rot))
+    kn, v = runs.view(n, heads, -1)[:, :, :dim], runs.view(n, heads, -1)[:, :, dim:dim + vdim]
     out = torch.zeros(n, heads * vdim, dtype=torch.bfloat16, device=DEV)
     scale = 1.3 / np.sqrt(dk)
-    ops.expanded_attention_bf16(q, kn, kr, v, out, ctx.cu_seqlens, len(lens), max(lens), heads, dim, rot, vdim, scale, window)
+    ops.expanded_attention_bf16(q, runs, out, ctx.cu_seqlens, len(lens), max(lens), heads, dim, rot, vdim, scale, window)
     got, at = f64(out).reshape(n, heads, vdim), 0
-    q64, kn64, v64, kr64 = f64(q).reshape(n, heads, dk), f64(kn).reshape(n, heads, dim), f64(v).reshape(n, heads, vdim), f64(kr)
+    q64, kn64, v64, kr64 = f64(q).reshape(n, heads, dk), f64(kn), f64(v), f64(kr)
     for L in lens:
         for i in range(L):
             lo = max(0, i - window + 1) if window else 0
