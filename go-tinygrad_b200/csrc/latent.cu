@@ -254,14 +254,17 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, int ldq, bf16* __restric
     }
     __syncthreads();                                            // barriers and row_pos
     auto load_page = [&](int buf, int p) {
-        if (warp != 0) return;
+        // every warp asks for its own share of the rows (a few lanes of one instruction): copies asked for by
+        // one warp alone hold that warp, and with it the block, for as long as the copy engine takes them in
         const bf16* src = kc + (size_t)table[p] * page_stride;
         const uint32_t dst = smem_u32(page_s + (size_t)buf * kPageTokens * ldr);
-        if (lane == 0) mbar_expect_tx(bars + 8 * buf, (uint32_t)(kPageTokens * D * 2));
-        __syncwarp();
+        if (tid == 0) mbar_expect_tx(bars + 8 * buf, (uint32_t)(kPageTokens * D * 2));
         if (test_waits) return;
-        for (int r = lane; r < kPageTokens; r += 32)
+        constexpr int kShare = kPageTokens / (kLatThreads / 32);
+        if (lane < kShare) {
+            const int r = warp * kShare + lane;
             bulk_row(dst + (uint32_t)(r * ldr * 2), src + (size_t)r * D, (uint32_t)(D * 2), bars + 8 * buf);
+        }
     };
     const int n_pages = page_hi - page_lo + 1;
     load_page(0, page_lo);
@@ -629,11 +632,11 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
         const int valid = min(kKTile, len - kt * kKTile);
         for (int idx = valid * (vdim / 2) + tid; idx < kKTile * (vdim / 2); idx += kExpThreads)
             reinterpret_cast<uint32_t*>(td + (idx / (vdim / 2)) * ldt + dim)[idx % (vdim / 2)] = 0u;
-        if (warp != 0) return;
-        if (lane == 0) mbar_expect_tx(bars + 8 * buf, (uint32_t)(valid * per * 2));
-        __syncwarp();
+        if (tid == 0) mbar_expect_tx(bars + 8 * buf, (uint32_t)(valid * per * 2));
         if (test_waits) return;
-        for (int r = lane; r < valid; r += 32)
+        constexpr int kShare = kKTile / (kExpThreads / 32);     // every warp asks for its own share of the keys
+        const int r = warp * kShare + lane;
+        if (lane < kShare && r < valid)
             bulk_row(smem_u32(td + r * ldt), kv + (size_t)(tok0 + kt * kKTile + r) * ldkv + (size_t)h * per, (uint32_t)(per * 2), bars + 8 * buf);
     };
     for (int st = 0; st < kStages - 1; ++st)
