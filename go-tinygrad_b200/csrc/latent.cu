@@ -585,7 +585,8 @@ expanded_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __res
     extern __shared__ __align__(128) unsigned char smem[];
     const int b = blockIdx.z, h = blockIdx.y;
     const int tok0 = cu_seqlens[b], len = cu_seqlens[b + 1] - tok0;
-    const int q0 = blockIdx.x * kQTile;
+    // the last queries of a sequence see the most keys: their blocks are started first
+    const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * kQTile;
     if (q0 >= len) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
