@@ -22,12 +22,11 @@
 
 namespace {
 // ---- route ----------------------------------------------------------------------
-// One block of four warps per token: the token's row is staged in shared memory as
-// float, every warp takes every fourth pair of experts (two dot products at a time,
-// lanes striding over the channels, the router's rows read coalesced), and thread 0
-// picks from the logits.
+// One block of eight warps per token: the token's row is staged in shared memory as
+// float, every warp takes every eighth expert (lanes striding over the channels, the
+// router's rows read coalesced), and thread 0 picks from the logits.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, const float* __restrict__ bias,
                  int* __restrict__ chosen, float* __restrict__ weights, int N, int H, int E, int top) {
     chain_release();
@@ -40,33 +39,25 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
     const T* xr = x + (size_t)n * ldx;
     for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = to_f32<T>(xr[i]);
     __syncthreads();
-    for (int e = 2 * warp; e < E; e += 8) {
-        const bool two = e + 1 < E;
-        const float* r0 = router + (size_t)e * H;
-        const float* r1 = router + (size_t)(two ? e + 1 : e) * H;
+    const int n_warps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += n_warps) {
+        // a warp an expert: two chains over alternate steps, four channels a lane and step where the row allows it,
+        // the loads of several steps in flight together
+        const float* r = router + (size_t)e * H;
         float s0 = 0.f, s1 = 0.f;
-        if (H % 128 == 0 && (reinterpret_cast<uintptr_t>(router) % 16) == 0) {
-            // four channels a lane and step, the loads of several steps in flight together
+        if (H % 256 == 0 && (reinterpret_cast<uintptr_t>(router) % 16) == 0) {
 #pragma unroll 4
-            for (int i = lane * 4; i < H; i += 128) {
-                const float4 v = *reinterpret_cast<const float4*>(xs + i);
-                const float4 a = *reinterpret_cast<const float4*>(r0 + i), b = *reinterpret_cast<const float4*>(r1 + i);
-                s0 = fmaf(v.x, a.x, s0); s0 = fmaf(v.y, a.y, s0); s0 = fmaf(v.z, a.z, s0); s0 = fmaf(v.w, a.w, s0);
-                s1 = fmaf(v.x, b.x, s1); s1 = fmaf(v.y, b.y, s1); s1 = fmaf(v.z, b.z, s1); s1 = fmaf(v.w, b.w, s1);
+            for (int i = lane * 4; i < H; i += 256) {
+                const float4 v0 = *reinterpret_cast<const float4*>(xs + i), v1 = *reinterpret_cast<const float4*>(xs + i + 128);
+                const float4 a = *reinterpret_cast<const float4*>(r + i), b = *reinterpret_cast<const float4*>(r + i + 128);
+                s0 = fmaf(v0.x, a.x, s0); s0 = fmaf(v0.y, a.y, s0); s0 = fmaf(v0.z, a.z, s0); s0 = fmaf(v0.w, a.w, s0);
+                s1 = fmaf(v1.x, b.x, s1); s1 = fmaf(v1.y, b.y, s1); s1 = fmaf(v1.z, b.z, s1); s1 = fmaf(v1.w, b.w, s1);
             }
         } else {
-            for (int i = lane; i < H; i += 32) {
-                const float v = xs[i];
-                s0 = fmaf(v, r0[i], s0);
-                s1 = fmaf(v, r1[i], s1);
-            }
+            for (int i = lane; i < H; i += 32) s0 = fmaf(xs[i], r[i], s0);
         }
-        s0 = warp_sum(s0);
-        s1 = warp_sum(s1);
-        if (lane == 0) {
-            z[e] = s0 + (bias ? bias[e] : 0.f);
-            if (two) z[e + 1] = s1 + (bias ? bias[e + 1] : 0.f);
-        }
+        s0 = warp_sum(s0 + s1);
+        if (lane == 0) z[e] = s0 + (bias ? bias[e] : 0.f);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -228,8 +219,8 @@ GTG_API int gtg_moe_route(int dtype, const void* x, int ldx, const float* router
     const size_t smem = (size_t)(H + E) * sizeof(float);
     if (smem > 48 * 1024) return kErrUnsupported;
     const dim3 grid(N);
-    if (dtype == 0) return launch_chained(moe_route_kernel<float>, grid, dim3(128), smem, stream, (const float*)x, ldx, router, bias, chosen, weights, N, H, E, top);
-    if (dtype == 1) return launch_chained(moe_route_kernel<bf16>, grid, dim3(128), smem, stream, (const bf16*)x, ldx, router, bias, chosen, weights, N, H, E, top);
+    if (dtype == 0) return launch_chained(moe_route_kernel<float>, grid, dim3(256), smem, stream, (const float*)x, ldx, router, bias, chosen, weights, N, H, E, top);
+    if (dtype == 1) return launch_chained(moe_route_kernel<bf16>, grid, dim3(256), smem, stream, (const bf16*)x, ldx, router, bias, chosen, weights, N, H, E, top);
     return kErrBadArgument;
 }
 

@@ -85,6 +85,19 @@ def test_plan_schedule_tensor_names_and_cache_requests():
     assert blocks[1].cache_requests() == [] and blocks[2].cache_requests() == [KVRequest(1, 8, 64, planes=1)]
 
 
+def test_several_layers_may_read_one_layers_latents_and_a_model_may_start_with_experts():
+    cfg = copy.deepcopy(CONFIG)
+    cfg["layers"][0]["mlp"], cfg["layers"][1]["mlp"] = cfg["layers"][1]["mlp"], cfg["layers"][0]["mlp"]
+    cfg["layers"][2]["mixer"] = mixer(4, 6, 4, 8, 10, 3, 0.1, 100.0, kv_from=0)      # a second reader of layer 0, its own heads and window
+    arch = find_architecture(cfg)
+    plan = arch.plan(arch.read_config(cfg))
+    assert [(e.layer, e.cache) for e in plan.schedule] == [(0, None), (1, 0), (2, 0)]
+    names = {s.name for s in plan_weight_specs(plan)}
+    assert "l0.mlp.router" in names and "l1.mlp.gate.b" in names and "l2.mix.dkv" not in names and "l2.mix.uk" in names
+    blocks = [build_part("block", layer.block) for layer in plan.layers]
+    assert [len(b.cache_requests()) for b in blocks] == [1, 0, 0]
+
+
 def test_yarn_frequencies_of_package_and_oracle_agree():
     for dims, base, scaling in [(8, 100.0, None), (16, 250.0, {"factor": 3.0, "original": 40, "fast": 4.0, "slow": 0.5}),
                                 (2, 7.0, {"factor": 4.0, "original": 16, "fast": 2.0, "slow": 1.0})]:
