@@ -62,7 +62,16 @@ CONFIG_S = {
         layer(mixer_json(2, 128, 32, 8, 96, 40, 0.08, 10000.0, kv_from=0), {"kind": "dense", "ff": 264}),
     ],
 }
-CONFIGS = {"R": (CONFIG_R, 3, 0.12, 0.1), "S": (CONFIG_S, 4, 0.08, 0.05)}     # configuration, seed, std, norm std
+# U: nothing is a multiple of 8, 4 or even 2 where the design allows it: every product, norm and attention takes
+# its plain kernel in both dtypes.
+CONFIG_U = {
+    "architecture": "Senupel", "vocab": 101, "width": 50, "norm": {"eps": 1e-5},
+    "layers": [
+        layer(mixer_json(3, 6, 2, 5, 7, 3, 0.4, 20.0), moe(9, 3, 2)),
+        layer(mixer_json(2, 5, 2, 9, 7, 70, 0.3, 20.0, kv_from=0), {"kind": "dense", "ff": 11}),
+    ],
+}
+CONFIGS = {"R": (CONFIG_R, 3, 0.12, 0.1), "S": (CONFIG_S, 4, 0.08, 0.05), "U": (CONFIG_U, 5, 0.15, 0.1)}     # configuration, seed, std, norm std
 
 
 @pytest.fixture(scope="module")
@@ -518,7 +527,7 @@ def test_routed_experts_choose_weigh_and_add_up(dtype, experts, top, hidden, ff,
 
 # ------------------------------------------------------------------- whole models
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["R", "S"])
+@pytest.mark.parametrize("name", ["R", "S", "U"])
 def test_whole_prompts_of_many_lengths(folders, name, dtype):
     model = get_model(folders, name, dtype)
     cache = model.new_cache(max_tokens=64 * 6)
@@ -546,7 +555,7 @@ def test_portions_down_to_two_tokens_and_token_by_token_from_the_start(folders, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["R", "S"])
+@pytest.mark.parametrize("name", ["R", "S", "U"])
 def test_long_decoding_across_page_borders_and_windows(folders, name, dtype):
     model = get_model(folders, name, dtype)
     cache = model.new_cache(max_tokens=64 * 6)
